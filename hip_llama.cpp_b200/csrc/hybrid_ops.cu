@@ -55,6 +55,24 @@ __global__ void hyb_dyt2_kernel(T* __restrict__ out1, T* __restrict__ out2, cons
   }
 }
 
+// layer norm: (x - mean) / sqrt(variance + eps) * w + b, the variance as the mean of the squared deviations (two passes
+// over the row, which the block keeps in registers / L1); one block per row
+template <typename T>
+__global__ void hyb_layernorm_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                     float eps, int width, const int* __restrict__ rows_idx) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows_idx ? rows_idx[r] : r) * width;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) sum += xr[i];
+  const float mean = block_sum(sum, red) / (float)width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) { const float d = xr[i] - mean; ss = fmaf(d, d, ss); }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) hyb_store(out + (size_t)r * width + i, fmaf((xr[i] - mean) * inv, w[i], b ? b[i] : 0.f));
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // linear: 64 x 64 output tile per block, 16-deep k slices through shared memory, 4 x 4 per thread, fp32 FMA in
 // ascending k: the sum of an output element is the same whatever tile or group it lands in.
@@ -272,32 +290,53 @@ __global__ void hyb_attn_prepare_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t 
     const bool is_q = h < a.heads;
     const float* src = pr + (is_q ? a.o_q + h * a.dim : a.o_k + (h - a.heads) * a.dim);
     float* dst = is_q ? q_out + (size_t)r * a.heads * a.dim + (size_t)h * a.dim : kv.k_pool + krow + (size_t)(h - a.heads) * a.dim;
-    // pairs (2i, 2i+1): rotated below `half`, passed through above
+    // the first rot_dims entries rotated (pairs by the layout), the rest passed through
+    const float* cr = cos_t + (size_t)r * half;
+    const float* sr = sin_t + (size_t)r * half;
     float ss = 0.f;
-    const int npairs = (a.dim + 1) / 2;
-    for (int i = lane; i < npairs; i += 32) {
-      float u = src[2 * i], v = 2 * i + 1 < a.dim ? src[2 * i + 1] : 0.f;
-      if (i < half) {
-        const float c = cos_t[(size_t)r * half + i], s = sin_t[(size_t)r * half + i];
-        const float nu = u * c - v * s, nv = v * c + u * s;
-        u = nu; v = nv;
-      }
-      ss = fmaf(u, u, ss);
-      ss = fmaf(v, v, ss);
-    }
+    for (int d = lane; d < a.dim; d += 32) { const float v = hyb_rotated(src, d, rot_dims, a.rot_layout, cr, sr); ss = fmaf(v, v, ss); }
     ss = warp_sum(ss);
     const float inv = a.unit_rms ? 1.0f / sqrtf(ss / (float)a.dim + a.eps) : 1.0f;
-    for (int i = lane; i < npairs; i += 32) {
-      float u = src[2 * i], v = 2 * i + 1 < a.dim ? src[2 * i + 1] : 0.f;
-      if (i < half) {
-        const float c = cos_t[(size_t)r * half + i], s = sin_t[(size_t)r * half + i];
-        const float nu = u * c - v * s, nv = v * c + u * s;
-        u = nu; v = nv;
-      }
-      dst[2 * i] = u * inv;
-      if (2 * i + 1 < a.dim) dst[2 * i + 1] = v * inv;
-    }
+    for (int d = lane; d < a.dim; d += 32) dst[d] = hyb_rotated(src, d, rot_dims, a.rot_layout, cr, sr) * inv;
   }
+}
+
+// What the attention kernels share beyond the causal block-of-positions rule.
+// Visibility of key t for a query at p whose block of positions starts at `first`:
+__device__ __forceinline__ bool hyb_attn_sees(const tha_attn_t& a, int t, int p, int first) {
+  return t <= p && t >= first && (a.window <= 0 || p - t < a.window || t < a.keep_first);
+}
+// The key tiles (of 32, aligned to absolute multiples of 32) a block of queries at positions p_first..p_last walks: all from
+// the tile of key_lo to the tile of p_last, except, under a window, the run of tiles that lie wholly between the kept first
+// keys and the window of the block's first query.  Logical tile i of n: kt = i < n_a ? begin + 32 i : resume + 32 (i - n_a).
+struct HybTiles { int begin, n_a, resume, n; };
+__device__ __forceinline__ HybTiles hyb_attn_tiles(const tha_attn_t& a, int key_lo, int p_first, int p_last) {
+  HybTiles t;
+  t.begin = (key_lo / 32) * 32;
+  t.n_a = 0;
+  t.resume = t.begin;
+  if (a.window > 0) {
+    const int win_lo = max(key_lo, p_first - a.window + 1);
+    const int keep_end = min(a.keep_first, p_last + 1);                                  // kept keys: [key_lo, keep_end)
+    const int after_kept = keep_end > key_lo ? ((keep_end - 1) / 32 + 1) * 32 : t.begin;  // first tile past them
+    const int wt = (win_lo / 32) * 32;
+    if (wt > after_kept) { t.n_a = (after_kept - t.begin) / 32; t.resume = wt; }
+  }
+  t.n = t.n_a + (p_last - t.resume) / 32 + 1;
+  return t;
+}
+// The end of a (query, head): with m, l the running maximum and sum, the factor the accumulator is multiplied by --
+// 1 / (l + exp(sink - m)) in a form that cannot overflow, times the head's output gate.
+__device__ __forceinline__ float hyb_attn_final_factor(const tha_attn_t& a, int h, float m, float l, const float* gate_row) {
+  float f;
+  if (a.sink) {
+    const float sk = a.sink[h], M = fmaxf(m, sk), e = expf(m - M);
+    f = e / (l * e + expf(sk - M));
+  } else {
+    f = 1.0f / l;
+  }
+  if (gate_row) f *= hyb_sigmoid(gate_row[h]);
+  return f;
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -312,7 +351,8 @@ constexpr int ATT_PAIRS = 16, ATT_KEYS = 32, ATT_MAX_VC = 16;   // value channel
 
 template <typename T, int VC>
 __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
-                                                       T* __restrict__ out, int AG, int AP, int splits, float* __restrict__ partial) {
+                                                       T* __restrict__ out, int AG, int AP, int splits, float* __restrict__ partial,
+                                                       const float* __restrict__ gate, long long ldg) {
   extern __shared__ __align__(16) float sm[];
   const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads;
   const bool vec = ((D | E) & 3) == 0;         // 128-bit shared-memory reads: rows padded to keep them aligned and conflict-free
@@ -345,7 +385,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
   }
   int my_pos[4], my_first[4];
   bool my_ok[4];
-  float m_run[4], l_run[4], acc[4][VC];
+  float m_run[4], l_run[4], acc[4][VC], my_scale[4];
 #pragma unroll
   for (int rr = 0; rr < 4; rr++) {
     const int pr = warp * 4 + rr;
@@ -353,6 +393,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     my_ok[rr] = r < r_end && hg < gsize;
     my_pos[rr] = p_first + pr / AG;
     my_first[rr] = a.chunk > 0 ? (my_pos[rr] / a.chunk) * a.chunk : 0;
+    my_scale[rr] = (a.head_scale && my_ok[rr]) ? a.head_scale[g * gsize + hg] : 1.0f;
     m_run[rr] = -INFINITY; l_run[rr] = 0.f;
 #pragma unroll
     for (int c = 0; c < VC; c++) acc[rr][c] = 0.f;
@@ -360,13 +401,15 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
   const int key_lo = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : 0;
   // with splits > 1 (few rows, long contexts) the key tiles are dealt to `splits` blocks in contiguous runs; each leaves
   // its running (max, sum, accumulator) in `partial` and hyb_attn_merge_kernel combines them in order
-  int kt_begin = (key_lo / ATT_KEYS) * ATT_KEYS, kt_last = p_last;
+  const HybTiles tiles = hyb_attn_tiles(a, key_lo, p_first, p_last);
+  int ti_begin = 0, ti_end = tiles.n;
   if (splits > 1) {
-    const int n_kt = (p_last - kt_begin) / ATT_KEYS + 1, per = (n_kt + splits - 1) / splits, sp = blockIdx.x % splits;
-    kt_last = min(p_last, kt_begin + (sp + 1) * per * ATT_KEYS - 1);
-    kt_begin += sp * per * ATT_KEYS;
+    const int per = (tiles.n + splits - 1) / splits, sp = blockIdx.x % splits;
+    ti_begin = sp * per;
+    ti_end = min(tiles.n, ti_begin + per);
   }
-  for (int kt = kt_begin; kt <= kt_last; kt += ATT_KEYS) {
+  for (int ti = ti_begin; ti < ti_end; ti++) {
+    const int kt = ti < tiles.n_a ? tiles.begin + ATT_KEYS * ti : tiles.resume + ATT_KEYS * (ti - tiles.n_a);
     __syncthreads();   // the previous tile is consumed (and Qs is written, the first time)
     // a warp fetches 8 keys: all 8 table entries first, then the rows four at a time into registers before any of them
     // goes to shared memory, so that the loads are in flight together (a load followed by its own store waits for it)
@@ -432,8 +475,8 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     const int t = kt + lane;
 #pragma unroll
     for (int rr = 0; rr < 4; rr++) {
-      const bool vis = my_ok[rr] && t <= my_pos[rr] && t >= my_first[rr];
-      const float sv = vis ? sc[rr] * a.scale : -INFINITY;
+      const bool vis = my_ok[rr] && hyb_attn_sees(a, t, my_pos[rr], my_first[rr]);
+      const float sv = vis ? sc[rr] * a.scale * my_scale[rr] : -INFINITY;
       const float m_new = fmaxf(m_run[rr], warp_max(sv));
       float p = 0.f, corr = 1.f;
       if (m_new > -INFINITY) {
@@ -502,7 +545,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
       if (lane == 0) { dst[E] = m_run[rr]; dst[E + 1] = l_run[rr]; }
       continue;
     }
-    const float inv = 1.0f / l_run[rr];
+    const float inv = hyb_attn_final_factor(a, h, m_run[rr], l_run[rr], gate ? gate + (size_t)r * ldg : nullptr);
 #pragma unroll
     for (int c = 0; c < VC; c++) {
       const int e = lane + 32 * c;
@@ -529,7 +572,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
                                                            __nv_bfloat16* __restrict__ out, int AG, int AP, int splits,
-                                                           float* __restrict__ partial) {
+                                                           float* __restrict__ partial, const float* __restrict__ gate, long long ldg) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads;
   const int KS = D + 8, VS = ATT_KEYS + 8;               // padded rows: conflict-free fragment reads
@@ -554,6 +597,7 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
   // this lane's two rows (pairs): A = 16 * warp + lr, B = A + 8
   int row_r[2], row_h[2], row_pos[2], row_first[2];
   bool row_ok[2];
+  float row_scale[2];
 #pragma unroll
   for (int x = 0; x < 2; x++) {
     const int pr = warp * 16 + lr + 8 * x;
@@ -563,6 +607,7 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
     row_ok[x] = pp < AP && row_r[x] < r_end && hg < gsize;
     row_pos[x] = p_first + pp;
     row_first[x] = a.chunk > 0 ? (row_pos[x] / a.chunk) * a.chunk : 0;
+    row_scale[x] = (a.head_scale && row_ok[x]) ? a.head_scale[row_h[x]] : 1.0f;
   }
   // q fragments: [k step][4]
   uint32_t qf[AM_MAXD / 16][4];
@@ -583,13 +628,15 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
 #pragma unroll
     for (int v = 0; v < 4; v++) oacc[n][v] = 0.f;
   const int key_lo = a.chunk > 0 ? (p_first / a.chunk) * a.chunk : 0;
-  int kt_begin = (key_lo / ATT_KEYS) * ATT_KEYS, kt_last = p_last;
+  const HybTiles tiles = hyb_attn_tiles(a, key_lo, p_first, p_last);
+  int ti_begin = 0, ti_end = tiles.n;
   if (splits > 1) {
-    const int n_kt = (p_last - kt_begin) / ATT_KEYS + 1, per = (n_kt + splits - 1) / splits, sp = blockIdx.x % splits;
-    kt_last = min(p_last, kt_begin + (sp + 1) * per * ATT_KEYS - 1);
-    kt_begin += sp * per * ATT_KEYS;
+    const int per = (tiles.n + splits - 1) / splits, sp = blockIdx.x % splits;
+    ti_begin = sp * per;
+    ti_end = min(tiles.n, ti_begin + per);
   }
-  for (int kt = kt_begin; kt <= kt_last; kt += ATT_KEYS) {
+  for (int ti = ti_begin; ti < ti_end; ti++) {
+    const int kt = ti < tiles.n_a ? tiles.begin + ATT_KEYS * ti : tiles.resume + ATT_KEYS * (ti - tiles.n_a);
     __syncthreads();
     // stage the tile: a warp takes 8 keys, four at a time through registers
     size_t krow[ATT_KEYS / 4];
@@ -656,8 +703,8 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
 #pragma unroll
         for (int y = 0; y < 2; y++) {
           const int t = kt + 8 * j + lc + y;
-          const bool vis = row_ok[x] && t <= row_pos[x] && t >= row_first[x];
-          const float sv = vis ? sacc[j][2 * x + y] * a.scale : -INFINITY;
+          const bool vis = row_ok[x] && hyb_attn_sees(a, t, row_pos[x], row_first[x]);
+          const float sv = vis ? sacc[j][2 * x + y] * a.scale * row_scale[x] : -INFINITY;
           sacc[j][2 * x + y] = sv;
           mx = fmaxf(mx, sv);
         }
@@ -707,7 +754,7 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
       if ((lane & 3) == 0) { dst[E] = m_run[x]; dst[E + 1] = l_run[x]; }
       continue;
     }
-    const float inv = 1.0f / l_run[x];
+    const float inv = hyb_attn_final_factor(a, row_h[x], m_run[x], l_run[x], gate ? gate + (size_t)row_r[x] * ldg : nullptr);
     __nv_bfloat16* dst = out + (size_t)row_r[x] * a.heads * E + (size_t)row_h[x] * E;
 #pragma unroll
     for (int n = 0; n < AM_MAXD / 8; n++)
@@ -717,7 +764,8 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
 
 // the splits of a (row, head) in ascending key order: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M); a warp each
 template <typename T>
-__global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int n_rows, int heads, int E, int splits) {
+__global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, int n_rows, int heads, int E, int splits,
+                                      tha_attn_t a, const float* __restrict__ gate, long long ldg) {
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (idx >= n_rows * heads) return;
   const size_t stride = (size_t)n_rows * heads * (E + 2);
@@ -729,10 +777,12 @@ __global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restri
   // lane s keeps split s's factor (at most 16 splits); splits that saw nothing have factor 0 and are not read
   float w = 0.f;
   if (lane < splits) { const float ms = p0[lane * stride + E]; w = ms > -INFINITY ? expf(ms - M) : 0.f; }
+  const int row = idx / heads, head = idx - row * heads;
+  const float fin = hyb_attn_final_factor(a, head, M, L, gate ? gate + (size_t)row * ldg : nullptr);
   for (int e = lane; e < E; e += 32) {
     float o = 0.f;
     for (int s = 0; s < splits; s++) { const float ws = __shfl_sync(THA_FULL_MASK, w, s); if (ws > 0.f) o = fmaf(p0[s * stride + e], ws, o); }
-    hyb_store(out + (size_t)idx * E + e, o / L);
+    hyb_store(out + (size_t)idx * E + e, o * fin);
   }
 }
 
@@ -1050,8 +1100,8 @@ __global__ void hyb_head_gate_kernel(T* __restrict__ out, const float* __restric
     inv = 1.0f / sqrtf(ss / (float)E + eps);
   }
   for (int e = lane; e < E; e += 32) {
-    const float z = gate[(size_t)r * ldg + h * E + e];
-    const float g = gate_act == THA_GATE_SILU ? z * hyb_sigmoid(z) : hyb_sigmoid(z);
+    const float z = gate ? gate[(size_t)r * ldg + h * E + e] : 0.f;
+    const float g = !gate ? 1.0f : gate_act == THA_GATE_SILU ? z * hyb_sigmoid(z) : hyb_sigmoid(z);
     const float v = do_norm ? o[e] * inv * norm[norm_per_head ? h * E + e : e] : o[e];
     hyb_store(out + (size_t)r * heads * E + (size_t)h * E + e, v * g);
   }
@@ -1266,6 +1316,7 @@ __global__ void hyb_route_groups_kernel(int experts, int top, int groups, int ke
 template <typename T>
 __global__ void hyb_ff_act_kernel(T* __restrict__ y, const float* __restrict__ gu, long long ldg, int col_g, int col_u, int n, int ff, int act,
                                   float limit, float alpha) {
+  // THA_ACT_XIELU reads its two stored numbers from (limit, alpha)
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)n * ff) return;
   const size_t r = i / ff; const int c = (int)(i - r * ff);
@@ -1274,6 +1325,8 @@ __global__ void hyb_ff_act_kernel(T* __restrict__ y, const float* __restrict__ g
   if (act == THA_ACT_RELU2) {
     const float p = fmaxf(u, 0.f);
     v = p * p;
+  } else if (act == THA_ACT_XIELU) {
+    v = u > 0.f ? fmaf(hyb_softplus(limit) * u, u, 0.5f * u) : fmaf(0.5f + hyb_softplus(alpha), expm1f(u) - u, 0.5f * u);
   } else if (act == THA_ACT_GELU_TANH_GLU) {
     const float g = gu[r * ldg + col_g + c];
     v = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
@@ -1341,6 +1394,16 @@ extern "C" int tha_hyb_rmsnorm(void* stream, int dtype, void* out, const float* 
 extern "C" int tha_hyb_norm(void* stream, int dtype, void* out, const float* x, const tha_norm_t* n, float eps, int n_rows, int width,
                             const int* rows_idx) {
   if (n->kind == THA_NORM_RMS) return tha_hyb_rmsnorm(stream, dtype, out, x, n->w, n->w_offset, eps, n_rows, width, rows_idx);
+  if (n->kind == THA_NORM_LAYER) {
+    if (!n->w) return THA_STATUS_INVALID_ARG;
+    if (n_rows < 1) return THA_STATUS_SUCCESS;
+    const int nt = pick_threads(width / 4);
+    if (dtype == THA_DT_BF16)
+      THA_CUDA_OK(launch(hyb_layernorm_kernel<bf16>, dim3(n_rows), dim3(nt), 0, (cudaStream_t)stream, false, (bf16*)out, x, n->w, n->b, eps, width, rows_idx));
+    else
+      THA_CUDA_OK(launch(hyb_layernorm_kernel<float>, dim3(n_rows), dim3(nt), 0, (cudaStream_t)stream, false, (float*)out, x, n->w, n->b, eps, width, rows_idx));
+    return THA_STATUS_SUCCESS;
+  }
   if (n->kind != THA_NORM_DYT || !n->w) return THA_STATUS_INVALID_ARG;
   if (n_rows < 1) return THA_STATUS_SUCCESS;
   const int nt = pick_threads(width);
@@ -1393,7 +1456,7 @@ extern "C" int tha_hyb_linear_heads(void* stream, int dtype, float* C, long long
 extern "C" int tha_hyb_head_gate(void* stream, int dtype, void* out, const float* o_raw, int n_rows, int heads, int E, int do_norm,
                                  float eps, const float* norm, int norm_per_head, const float* gate, long long ldg, int gate_act) {
   if (n_rows < 1) return THA_STATUS_SUCCESS;
-  if (!gate || (do_norm && !norm)) return THA_STATUS_INVALID_ARG;
+  if (do_norm && !norm) return THA_STATUS_INVALID_ARG;
   const dim3 grid(ceil_div(n_rows * heads, 4));
   if (dtype == THA_DT_BF16)
     THA_CUDA_OK(launch(hyb_head_gate_kernel<bf16>, grid, dim3(128), 0, (cudaStream_t)stream, false, (bf16*)out, o_raw, n_rows, heads, E, eps, norm,
@@ -1467,13 +1530,30 @@ int hyb_attn_wide_launch(cudaStream_t s, const tha_attn_t* a, const tha_rows_t* 
 
 extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
                             void* out, float* split_scratch, size_t split_scratch_floats) {
+  return tha_hyb_attn_gated(stream, dtype, a, rows, kv, q, out, split_scratch, split_scratch_floats, nullptr, 0);
+}
+
+// THA_HYB_ATTN_TC=0 keeps attention on the fp32 cores in the bf16 number format as well (A/B aid)
+static bool hyb_tc_attn() {
+  static int on = -1;
+  if (on < 0) { const char* v = getenv("THA_HYB_ATTN_TC"); on = (v && *v) ? atoi(v) != 0 : 1; }
+  return on != 0;
+}
+
+extern "C" int tha_hyb_attn_gated(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
+                                  void* out, float* split_scratch, size_t split_scratch_floats, const float* proj, long long ldp) {
   if (rows->n_rows < 1) return THA_STATUS_SUCCESS;
+  if (a->window < 0 || a->keep_first < 0) return THA_STATUS_INVALID_ARG;
+  const float* gate = (a->head_gate && proj) ? proj + a->o_g : nullptr;
+  const long long ldg = ldp;
+  // what the wide form does not know: windows, sinks, per-head scales and gates
+  const bool plain = a->window == 0 && !a->sink && !a->head_scale && !gate;
   if (a->heads % a->kv_heads || a->vdim > 32 * ATT_MAX_VC) return THA_STATUS_NOT_SUPPORTED;
   const int gsize = a->heads / a->kv_heads;
   // bf16 with heads the tensor-core form covers: 64 pairs per block; else 16 pairs on the fp32 cores
-  const bool tc = dtype == THA_DT_BF16 && hyb_tc_linear() && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= AM_MAXD && a->vdim <= AM_MAXD &&
+  const bool tc = dtype == THA_DT_BF16 && !a->fp32_scores && hyb_tc_linear() && hyb_tc_attn() && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= AM_MAXD && a->vdim <= AM_MAXD &&
                   (a->heads * a->vdim) % 2 == 0;
-  const bool wide = !tc && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_attn_wide_ok(a);
+  const bool wide = !tc && plain && !a->fp32_scores && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && hyb_attn_wide_ok(a);
   const int pairs = wide ? hyb_attn_wide_pairs(a, rows) : tc ? AM_PAIRS : ATT_PAIRS;
   const int AG = gsize < pairs ? gsize : pairs, AP = pairs / AG;
   const size_t smem = tc ? sizeof(__nv_bfloat16) * ((size_t)ATT_KEYS * (a->dim + 8) + (size_t)a->vdim * (ATT_KEYS + 8))
@@ -1482,7 +1562,9 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
   // position tiles: at most one ragged tile per sequence beyond rows / AP
   const int tiles = rows->n_rows / AP + rows->n_seqs;
   // few blocks and many keys (decoding at long contexts): deal the key tiles of a block to several
-  const int seen = rows->max_pos + 1, max_keys = a->chunk > 0 && a->chunk < seen ? a->chunk : seen;
+  const int seen = rows->max_pos + 1;
+  int max_keys = a->chunk > 0 && a->chunk < seen ? a->chunk : seen;
+  if (a->window > 0 && a->window + a->keep_first + 2 * ATT_KEYS < max_keys) max_keys = a->window + a->keep_first + 2 * ATT_KEYS;
   int splits = 1;
   const long long blocks = (long long)tiles * a->kv_heads * ceil_div(gsize, AG);
   if (split_scratch && blocks < 4 * 148 && max_keys >= 4 * ATT_KEYS) {
@@ -1498,30 +1580,30 @@ extern "C" int tha_hyb_attn(void* stream, int dtype, const tha_attn_t* a, const 
       const int st = hyb_attn_wide_launch(s, a, rows, kv, q, (bf16*)out, grid, pairs, AG, AP, splits, split_scratch);
       if (st != THA_STATUS_SUCCESS) return st;
     } else if (tc) {
-      THA_CUDA_OK(launch(hyb_attn_mma_kernel, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+      THA_CUDA_OK(launch(hyb_attn_mma_kernel, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch, gate, ldg));
     } else {
       if (a->vdim <= 256) {
         if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        THA_CUDA_OK(launch(hyb_attn_kernel<bf16, 8>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+        THA_CUDA_OK(launch(hyb_attn_kernel<bf16, 8>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch, gate, ldg));
       } else {
         if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        THA_CUDA_OK(launch(hyb_attn_kernel<bf16, 16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch));
+        THA_CUDA_OK(launch(hyb_attn_kernel<bf16, 16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch, gate, ldg));
       }
     }
     if (splits > 1)
       THA_CUDA_OK(launch(hyb_attn_merge_kernel<bf16>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (bf16*)out,
-                         (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits));
+                         (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits, *a, gate, ldg));
   } else {
     if (a->vdim <= 256) {
       if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<float, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      THA_CUDA_OK(launch(hyb_attn_kernel<float, 8>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch));
+      THA_CUDA_OK(launch(hyb_attn_kernel<float, 8>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch, gate, ldg));
     } else {
       if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<float, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      THA_CUDA_OK(launch(hyb_attn_kernel<float, 16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch));
+      THA_CUDA_OK(launch(hyb_attn_kernel<float, 16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (float*)out, AG, AP, splits, split_scratch, gate, ldg));
     }
     if (splits > 1)
       THA_CUDA_OK(launch(hyb_attn_merge_kernel<float>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (float*)out,
-                         (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits));
+                         (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits, *a, gate, ldg));
   }
   return THA_STATUS_SUCCESS;
 }

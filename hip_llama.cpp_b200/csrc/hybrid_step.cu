@@ -14,14 +14,19 @@
 
 namespace tha {
 
-// x = embed[token] (+ the learned vector of the row's position when the model has a position table)
+// x = embed[token] * scale (+ the learned vector of the row's position when the model has a position table); x0, when given,
+// keeps a copy of it for the layers that add the embedding output again
 template <typename T>
 __global__ void hyb_embed_kernel(float* __restrict__ x, const T* __restrict__ embed, const int* __restrict__ token, int width,
-                                 const T* __restrict__ pos_embed, const int* __restrict__ pos) {
+                                 const T* __restrict__ pos_embed, const int* __restrict__ pos, float scale, float* __restrict__ x0) {
   const int r = blockIdx.x;
   const T* e = embed + (size_t)token[r] * width;
   const T* p = pos_embed ? pos_embed + (size_t)pos[r] * width : nullptr;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)r * width + i] = hyb_load(e + i) + (p ? hyb_load(p + i) : 0.f);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = hyb_load(e + i) * scale + (p ? hyb_load(p + i) : 0.f);
+    x[(size_t)r * width + i] = v;
+    if (x0) x0[(size_t)r * width + i] = v;
+  }
 }
 
 // x += scale_mix * mixer + scale_ff * feed-forward (layer scales optional).  Two-sided mixers: each side's projection is normed over the width with its own weight,
@@ -90,7 +95,7 @@ struct Carver {
 
 struct StepBuffers {
   float *x, *proj, *q, *left, *right, *conv, *dt_raw, *gate_raw, *gu, *down, *sdown, *weight, *oraw, *split; size_t split_floats;
-  float *proj2, *qfull;
+  float *proj2, *qfull, *x0;
   void *h, *h2, *cq, *qplain, *abuf, *mbuf, *y, *sy, *hn, *hg;
   int *expert_id, *group_off, *sorted_row, *inv;
   float* cos_t[16]; float* sin_t[16];
@@ -111,10 +116,19 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
   const size_t W = m->width, es = m->dtype == THA_DT_BF16 ? 2 : 4;
   size_t n_in = 0, qd = 0, av = 0, mv = 0, cc = 0, dd = 0, dg = 0, gu = 0, ff = 0, sff = 0, top = 0, ne = 0;
   size_t n_in2 = 0, qr = 0, qf = 0, qp = 0;
-  bool norm2 = false;
+  bool norm2 = false, keep_embed = false;
   for (int i = 0; i < m->n_layers; i++) {
     const tha_hyb_layer_t& L = m->layers[i];
     n_in = max(n_in, (size_t)L.n_in);
+    if (L.pre_add_embed) keep_embed = true;
+    if (L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) {
+      qd = max(qd, (size_t)L.attn.heads * L.attn.dim);
+      av = max(av, (size_t)L.attn.heads * L.attn.vdim);
+    }
+    if (L.mixer == THA_MIX_ATTN_GDELTA) {
+      dd = max(dd, (size_t)L.gdelta.heads * L.gdelta.dim);
+      mv = max(mv, (size_t)L.gdelta.heads * L.gdelta.dim);
+    }
     if (L.mixer == THA_MIX_PARALLEL) {
       qd = max(qd, (size_t)L.attn.heads * L.attn.dim);
       av = max(av, (size_t)L.attn.heads * L.attn.vdim);
@@ -148,6 +162,8 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
     }
   }
   b->x = c.take<float>(R * W);
+  b->x0 = c.take<float>(keep_embed ? R * W : 0);
+  if (!keep_embed) b->x0 = nullptr;
   b->h = c.take<char>(R * W * es);
   b->proj = c.take<float>(R * n_in);
   b->h2 = c.take<char>(norm2 ? R * W * es : 0);
@@ -220,23 +236,40 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
   }
   carve(m, R, n_want, sc.base, &b);
 
+  const float embed_scale = m->embed_scale != 0.f ? m->embed_scale : 1.0f;
   if (dt == THA_DT_BF16)
     THA_CUDA_OK(launch(hyb_embed_kernel<bf16>, dim3(R), dim3(128), 0, s, false, b.x, (const bf16*)m->embed, rows->token, W, (const bf16*)m->pos_embed,
-                       rows->pos));
+                       rows->pos, embed_scale, b.x0));
   else
     THA_CUDA_OK(launch(hyb_embed_kernel<float>, dim3(R), dim3(128), 0, s, false, b.x, (const float*)m->embed, rows->token, W,
-                       (const float*)m->pos_embed, rows->pos));
+                       (const float*)m->pos_embed, rows->pos, embed_scale, b.x0));
   for (int i = 0; i < m->n_rot; i++) HYB_OK(tha_hyb_rotary_table(stream, &m->rot[i], rows->pos, R, b.cos_t[i], b.sin_t[i]));
 
   for (int li = 0; li < m->n_layers; li++) {
     const tha_hyb_layer_t& L = m->layers[li];
     const long long ldp = L.n_in;
-    const bool two_norms = L.has_norm2 && L.has_ff != THA_FF_NONE;
-    if (two_norms) HYB_OK(tha_hyb_norm_pair(stream, dt, b.h, b.h2, b.x, &L.norm1, &L.norm2, m->eps, R, W));
+    const bool seq = L.block == THA_BLOCK_SEQUENTIAL;
+    const bool two_norms = !seq && L.has_norm2 && L.has_ff != THA_FF_NONE;
+    if (seq && (L.pre_add_embed || L.pre_vec))   // a pass's re-entry addends and the mixer's norm in one pass over x
+      HYB_OK(tha_hyb_add_norm(stream, dt, b.x, nullptr, 0.f, nullptr, 0.f, L.pre_add_embed ? b.x0 : nullptr, L.pre_vec, &L.norm1, m->eps, b.h, R, W));
+    else if (two_norms) HYB_OK(tha_hyb_norm_pair(stream, dt, b.h, b.h2, b.x, &L.norm1, &L.norm2, m->eps, R, W));
     else HYB_OK(tha_hyb_norm(stream, dt, b.h, b.x, &L.norm1, m->eps, R, W, nullptr));
     HYB_OK(tha_hyb_linear(stream, dt, b.proj, ldp, b.h, W, 0, nullptr, L.w_in, 0, R, L.n_in, W, nullptr, 0));
     const float* right = nullptr;
-    if (L.mixer == THA_MIX_PARALLEL) {
+    if (L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) {
+      const tha_attn_t& a = L.attn;
+      const int rd = a.rot >= 0 ? m->rot[a.rot].dims : 0;
+      HYB_OK(tha_hyb_attn_prepare(stream, &a, rows, kv, b.proj, ldp, a.rot >= 0 ? b.cos_t[a.rot] : nullptr,
+                                  a.rot >= 0 ? b.sin_t[a.rot] : nullptr, rd, b.q));
+      HYB_OK(tha_hyb_attn_gated(stream, dt, &a, rows, kv, b.q, b.abuf, b.split_floats ? b.split : nullptr, b.split_floats, b.proj, ldp));
+      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.abuf, a.heads * a.vdim, 0, nullptr, a.w_o, 0, R, W, a.heads * a.vdim, nullptr, 0));
+      if (L.mixer == THA_MIX_ATTN_GDELTA) {
+        const tha_gdelta_t& g = L.gdelta;
+        HYB_OK(tha_hyb_gdelta_scan(stream, dt, &g, rows, st, b.proj, ldp, b.dt_raw, b.oraw, b.mbuf));
+        HYB_OK(tha_hyb_linear(stream, dt, b.right, W, b.mbuf, g.heads * g.dim, 0, nullptr, g.w_o, 0, R, W, g.heads * g.dim, nullptr, 0));
+        right = b.right;
+      }
+    } else if (L.mixer == THA_MIX_PARALLEL) {
       const tha_attn_t& a = L.attn;
       const int rd = a.rot >= 0 ? m->rot[a.rot].dims : 0;
       HYB_OK(tha_hyb_attn_prepare(stream, &a, rows, kv, b.proj, ldp, a.rot >= 0 ? b.cos_t[a.rot] : nullptr,
@@ -267,8 +300,12 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       const float* sn = a.rot >= 0 ? b.sin_t[a.rot] : nullptr;
       const int per = a.dim + a.rot_dim, DA = a.kv_rank + a.rot_dim;
       HYB_OK(tha_hyb_latent_prepare(stream, dt, &a, rows, kv, b.proj, ldp, cs, sn, rd, b.cq));
-      HYB_OK(tha_hyb_linear(stream, dt, b.qfull, a.heads * per, b.cq, a.q_rank, 0, nullptr, a.w_uq, 0, R, a.heads * per, a.q_rank, nullptr, 0));
-      HYB_OK(tha_hyb_latent_split_q(stream, dt, &a, R, b.qfull, cs, sn, rd, b.qplain, b.q));
+      if (a.direct_q) {   // the queries are columns of the stacked projection
+        HYB_OK(tha_hyb_latent_split_q(stream, dt, &a, R, b.proj + a.o_q, ldp, cs, sn, rd, b.qplain, b.q));
+      } else {
+        HYB_OK(tha_hyb_linear(stream, dt, b.qfull, a.heads * per, b.cq, a.q_rank, 0, nullptr, a.w_uq, 0, R, a.heads * per, a.q_rank, nullptr, 0));
+        HYB_OK(tha_hyb_latent_split_q(stream, dt, &a, R, b.qfull, 0, cs, sn, rd, b.qplain, b.q));
+      }
       // keys absorbed into the queries: q_abs[h, 0:kv_rank] = W_uk[h]^T q_plain[h]
       HYB_OK(tha_hyb_linear_heads(stream, dt, b.q, (long long)a.heads * DA, DA, b.qplain, (long long)a.heads * a.dim, a.dim, 0, a.w_uk_t,
                                   (long long)a.kv_rank * a.dim, R, a.kv_rank, a.dim, a.heads));
@@ -276,16 +313,40 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       tha_attn_t at = {};
       at.heads = a.heads; at.kv_heads = 1; at.dim = DA; at.vdim = a.kv_rank; at.rot = -1; at.unit_rms = 0; at.eps = a.eps;
       at.scale = a.scale; at.chunk = 0; at.cache_layer = a.cache_layer; at.values_in_keys = 1;
+      at.window = a.window; at.sink = a.sink; at.fp32_scores = a.fp32_scores;
       tha_kv_t lkv = *kv;
       lkv.v_pool = kv->k_pool;
       HYB_OK(tha_hyb_attn(stream, dt, &at, rows, &lkv, b.q, b.abuf, b.split_floats ? b.split : nullptr, b.split_floats));
       // values expanded per head: o[h] = W_uv[h] o_latent[h]
       HYB_OK(tha_hyb_linear_heads(stream, dt, b.oraw, (long long)a.heads * a.vdim, a.vdim, b.abuf, (long long)a.heads * a.kv_rank, a.kv_rank, 0,
                                   a.w_uv, (long long)a.vdim * a.kv_rank, R, a.vdim, a.kv_rank, a.heads));
-      HYB_OK(tha_hyb_head_gate(stream, dt, b.mbuf, b.oraw, R, a.heads, a.vdim, 0, a.eps, nullptr, 0, b.proj + a.o_g, ldp, THA_GATE_SIGMOID));
+      HYB_OK(tha_hyb_head_gate(stream, dt, b.mbuf, b.oraw, R, a.heads, a.vdim, 0, a.eps, nullptr, 0, a.no_gate ? nullptr : b.proj + a.o_g, ldp,
+                               THA_GATE_SIGMOID));
       HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, a.heads * a.vdim, 0, nullptr, a.w_o, 0, R, W, a.heads * a.vdim, nullptr, 0));
     } else {
       return THA_STATUS_NOT_SUPPORTED;
+    }
+    if (seq) {
+      // x += m * mixer and the feed-forward's norm of the new x in one pass; the feed-forward; then its residual add, the
+      // side input and the tap in one more
+      const float m_res = L.res_mult;
+      const float cl = L.mixer == THA_MIX_ATTN_GDELTA ? m_res * L.mix_left : m_res, cr = m_res * L.mix_right;
+      const float* ffo = nullptr;
+      if (L.has_ff == THA_FF_DENSE) {
+        const tha_dense_ff_t& d = L.dense;
+        HYB_OK(tha_hyb_add_norm(stream, dt, b.x, b.left, cl, right, cr, nullptr, nullptr, &L.norm2, m->eps, b.h2, R, W));
+        HYB_OK(tha_hyb_linear(stream, dt, b.proj2, L.n_in2, b.h2, W, 0, nullptr, L.w_in2, 0, R, L.n_in2, W, nullptr, 0));
+        HYB_OK(tha_hyb_ff_act(stream, dt, d.act, b.sy, b.proj2, L.n_in2, d.o_gate, d.o_up, R, d.ff, d.act_p, d.act_q));
+        HYB_OK(tha_hyb_linear(stream, dt, b.sdown, W, b.sy, d.ff, 0, nullptr, d.w_down, 0, R, W, d.ff, nullptr, 0));
+        ffo = b.sdown;
+      } else if (L.has_ff == THA_FF_NONE) {
+        HYB_OK(tha_hyb_add_norm(stream, dt, b.x, b.left, cl, right, cr, nullptr, nullptr, nullptr, m->eps, nullptr, R, W));
+      } else {
+        return THA_STATUS_NOT_SUPPORTED;
+      }
+      HYB_OK(tha_hyb_side_finish(stream, dt, b.x, ffo, m_res, &L.side, m->side_table, m->side_cols, rows->token, m->eps, R, W,
+                                 taps ? taps + (size_t)li * R * W : (float*)nullptr));
+      continue;
     }
     // the feed-forward reads the mixer's normed input, or a second norm of the same x through its own stacked product
     const void* hf = b.h;

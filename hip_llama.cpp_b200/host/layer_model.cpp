@@ -16,6 +16,7 @@
 
 void register_timerax();   // host/arch_timerax.cpp
 void register_numizen();   // host/arch_numizen.cpp
+void register_bozovik();   // host/arch_bozovik.cpp
 
 // ---- registry -----------------------------------------------------------------------------------------------------
 static std::vector<ArchitectureEntry>& registry() {
@@ -28,6 +29,7 @@ static void register_builtin() {
     registry().push_back({"llama2", ModelFamily::Llama2Checkpoint, nullptr});   // llama2.c v0 / v2 checkpoint files (host/utils.cpp)
     register_timerax();
     register_numizen();
+    register_bozovik();
   });
 }
 void register_architecture(const ArchitectureEntry& e) {
@@ -232,7 +234,10 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       n.kind = spec.norm_kind;
       n.w = vec(name, W);
       n.w_offset = 1.0f;
-      if (spec.norm_kind == THA_NORM_DYT) {
+      if (spec.norm_kind == THA_NORM_LAYER) {
+        n.w_offset = 0.0f;
+        n.b = vec(name + ".b", W);
+      } else if (spec.norm_kind == THA_NORM_DYT) {
         n.w_offset = 0.0f;
         n.b = vec(name + ".b", W);
         std::vector<float> a;
@@ -270,6 +275,47 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       }
       return (int)r;
     };
+    // softmax attention (alone, or as one side of a two-sided mixer): its matrices into the stack, its options
+    auto attention = [&](const AttnSpec& a, Stack& in, tha_attn_t& A) {
+      if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads) throw std::runtime_error("attention: heads must be a multiple of kv_heads");
+      if (a.dim < 1 || a.vdim < 1) throw std::runtime_error("attention: dim and vdim must be positive");
+      if (a.window < 0 || a.keep_first < 0) throw std::runtime_error("attention: the window and the kept first tokens cannot be negative");
+      A.heads = a.heads; A.kv_heads = a.kv_heads; A.dim = a.dim; A.vdim = a.vdim;
+      A.unit_rms = a.unit_rms; A.eps = spec.eps; A.scale = a.scale; A.chunk = a.chunk;
+      A.window = a.window; A.keep_first = a.window > 0 ? a.keep_first : 0;
+      A.fp32_scores = a.fp32_scores;
+      A.rot = -1;
+      if (a.rotary && a.rot.dims > 0) {
+        if (a.rot.dims > a.dim || (a.rot.dims & 1)) throw std::runtime_error("attention: rotated dimensions must be even and at most dim");
+        A.rot = rotary(a.rot);
+        A.rot_layout = a.rot.halves ? THA_ROT_HALVES : THA_ROT_INTERLEAVED;
+      }
+      A.cache_layer = m->n_cache_layers_++;
+      m->separate_values_ = true;
+      m->kv_dim_ = std::max(m->kv_dim_, std::max(a.kv_heads * a.dim, a.kv_heads * a.vdim));
+      A.o_q = in.add(a.q, (long long)a.heads * a.dim);
+      A.o_k = in.add(a.k, (long long)a.kv_heads * a.dim);
+      A.o_v = in.add(a.v, (long long)a.kv_heads * a.vdim);
+      if (!a.g.empty()) { A.head_gate = 1; A.o_g = in.add(a.g, a.heads); }
+      if (!a.sink.empty()) A.sink = vec(a.sink, a.heads);
+      else if (a.sink_zero) { std::vector<float> z(a.heads, 0.f); A.sink = (const float*)m->upload(z.data(), z.size() * 4); }
+      if (!a.temp.empty()) A.head_scale = vec(a.temp, a.heads);
+      A.w_o = mat(a.o, W, a.heads * a.vdim);
+    };
+    // row `row` of a [rows, width] tensor as an fp32 device vector (uploaded once per tensor)
+    std::map<std::string, const float*> pre_tables;
+    auto pre_vector = [&](const std::string& name, int row) -> const float* {
+      const TensorInfo& t = file.info(name);
+      if (t.shape.size() != 2 || t.shape[1] != W || row < 0 || row >= t.shape[0])
+        throw std::runtime_error("tensor '" + name + "': row " + std::to_string(row) + " of [rows, width] is asked for");
+      auto it = pre_tables.find(name);
+      if (it == pre_tables.end()) {
+        std::vector<float> v;
+        file.read_f32(name, &v);
+        it = pre_tables.emplace(name, (const float*)m->upload(v.data(), v.size() * 4)).first;
+      }
+      return it->second + (size_t)row * W;
+    };
     m->layers_.resize(spec.layers.size());
     long long state = 0;
     for (size_t li = 0; li < spec.layers.size(); li++) {
@@ -279,7 +325,16 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         // another run of an earlier entry: the same device weights, a cache layer and state of its own
         if ((size_t)ls.same_weights_as >= li) throw std::runtime_error("a repeated layer must follow the layer it repeats");
         L = m->layers_[ls.same_weights_as];
-        if (L.mixer == THA_MIX_PARALLEL) {
+        L.pre_add_embed = ls.pre_add_embed ? 1 : 0;
+        L.pre_vec = nullptr;
+        if (!ls.pre_vec.empty()) L.pre_vec = pre_vector(ls.pre_vec, ls.pre_vec_row);
+        if (L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) {
+          L.attn.cache_layer = m->n_cache_layers_++;
+          if (L.mixer == THA_MIX_ATTN_GDELTA) {
+            L.gdelta.state_off = state;
+            state += tha_hyb_gdelta_state_floats(L.gdelta.heads, L.gdelta.dim);
+          }
+        } else if (L.mixer == THA_MIX_PARALLEL) {
           L.attn.cache_layer = m->n_cache_layers_++;
           L.mem.state_off = state;
           state += (long long)L.mem.heads * ((long long)L.mem.dim * L.mem.vdim + L.mem.dim + 1);
@@ -298,6 +353,12 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       }
       memset(&L, 0, sizeof(L));
       L.mixer = ls.mixer;
+      L.block = ls.block;
+      L.res_mult = ls.res_mult;
+      L.pre_add_embed = ls.pre_add_embed ? 1 : 0;
+      if (!ls.pre_vec.empty()) L.pre_vec = pre_vector(ls.pre_vec, ls.pre_vec_row);
+      if (ls.block == THA_BLOCK_SEQUENTIAL && ls.has_ff && (ls.ff_kind != THA_FF_DENSE || ls.norm2.empty()))
+        throw std::runtime_error("a sequential block serves a dense feed-forward behind a second norm, or none");
       L.norm1 = norm(ls.norm1);
       if (!ls.scale_mix.empty()) L.scale_mix = vec(ls.scale_mix, W);
       if (!ls.scale_ff.empty() && ls.has_ff) L.scale_ff = vec(ls.scale_ff, W);
@@ -305,24 +366,35 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       Stack in2(file, dtype, W);                       // what reads the second norm
       const bool two = !ls.norm2.empty() && ls.has_ff;
       Stack& fin = two ? in2 : in;                     // where the feed-forward's input matrices go
-      if (ls.mixer == THA_MIX_PARALLEL) {
-        const AttnSpec& a = ls.attn;
-        if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads) throw std::runtime_error("attention: heads must be a multiple of kv_heads");
-        tha_attn_t& A = L.attn;
-        A.heads = a.heads; A.kv_heads = a.kv_heads; A.dim = a.dim; A.vdim = a.vdim;
-        A.unit_rms = a.unit_rms; A.eps = spec.eps; A.scale = a.scale; A.chunk = a.chunk;
-        A.rot = -1;
-        if (a.rotary && a.rot.dims > 0) {
-          if (a.rot.dims > a.dim || (a.rot.dims & 1)) throw std::runtime_error("attention: rotated dimensions must be even and at most dim");
-          A.rot = rotary(a.rot);
+      if (ls.mixer == THA_MIX_ATTN || ls.mixer == THA_MIX_ATTN_GDELTA) {
+        attention(ls.attn, in, L.attn);
+        if (ls.mixer == THA_MIX_ATTN_GDELTA) {
+          const GDeltaSpec& g = ls.gdelta;
+          if (g.heads < 1 || g.dim < 1) throw std::runtime_error("generalized delta rule: heads and dim must be positive");
+          if (g.dim > 256) throw std::runtime_error("generalized delta rule: more than 256 key channels per head are not served");
+          tha_gdelta_t& G = L.gdelta;
+          G.heads = g.heads; G.dim = g.dim; G.eps = spec.eps;
+          const TensorInfo& w1 = file.info(g.w1);
+          if (w1.shape.size() != 2) throw std::runtime_error("generalized delta rule: the decay projection must be a matrix");
+          G.rank = (int)w1.shape[0];
+          const long long hd = (long long)g.heads * g.dim;
+          G.o_r = in.add(g.r, hd);
+          G.o_k = in.add(g.k, hd);
+          G.o_v = in.add(g.v, hd);
+          G.o_g = in.add(g.g, hd);
+          G.o_a = in.add(g.a, hd);
+          G.o_w1 = in.add(g.w1, G.rank);
+          G.w_w2 = mat(g.w2, hd, G.rank);
+          G.w0 = vec(g.w0, (size_t)hd);
+          G.a_b = vec(g.a_b, (size_t)hd);
+          G.norm = vec(g.norm, (size_t)hd);
+          G.w_o = mat(g.o, W, (int)hd);
+          G.state_off = state;
+          state += tha_hyb_gdelta_state_floats(g.heads, g.dim);
+          L.mix_left = ls.mix_left; L.mix_right = ls.mix_right;
         }
-        A.cache_layer = m->n_cache_layers_++;
-        m->separate_values_ = true;
-        m->kv_dim_ = std::max(m->kv_dim_, std::max(a.kv_heads * a.dim, a.kv_heads * a.vdim));
-        A.o_q = in.add(a.q, (long long)a.heads * a.dim);
-        A.o_k = in.add(a.k, (long long)a.kv_heads * a.dim);
-        A.o_v = in.add(a.v, (long long)a.kv_heads * a.vdim);
-        A.w_o = mat(a.o, W, a.heads * a.vdim);
+      } else if (ls.mixer == THA_MIX_PARALLEL) {
+        attention(ls.attn, in, L.attn);
         const MemSpec& r = ls.mem;
         tha_mem_t& M = L.mem;
         M.heads = r.heads; M.dim = r.dim; M.vdim = r.vdim; M.gate_cap = r.gate_cap; M.eps = spec.eps;
@@ -395,7 +467,8 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         state += (long long)g.heads * g.dim * ((g.vdim + 7) / 8 * 8);   // value columns padded to eights
       } else if (ls.mixer == THA_MIX_LATENT) {
         const LatentSpec& a = ls.latent;
-        if (a.heads < 1 || a.dim < 1 || a.vdim < 1 || a.q_rank < 1 || a.kv_rank < 1 || a.rot_dim < 0)
+        const bool direct_q = !a.q.empty();
+        if (a.heads < 1 || a.dim < 1 || a.vdim < 1 || (!direct_q && a.q_rank < 1) || a.kv_rank < 1 || a.rot_dim < 0 || a.window < 0)
           throw std::runtime_error("latent attention: heads, dim, vdim, q_rank and kv_rank must be positive");
         tha_latent_t& A = L.latent;
         A.heads = a.heads; A.dim = a.dim; A.rot_dim = a.rot_dim; A.vdim = a.vdim; A.q_rank = a.q_rank; A.kv_rank = a.kv_rank;
@@ -404,15 +477,28 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         if (a.rotary && a.rot.dims > 0 && a.rot_dim > 0) {
           if (a.rot.dims > a.rot_dim || (a.rot.dims & 1)) throw std::runtime_error("latent attention: rotated dimensions must be even and at most rot_dim");
           A.rot = rotary(a.rot);
+          A.rot_layout = a.rot.halves ? THA_ROT_HALVES : THA_ROT_INTERLEAVED;
         }
         A.cache_layer = m->n_cache_layers_++;
         m->kv_dim_ = std::max(m->kv_dim_, a.kv_rank + a.rot_dim);
-        A.o_dq = in.add(a.dq, a.q_rank);
+        A.window = a.window;
+        A.fp32_scores = a.fp32_scores;
+        if (!a.sink.empty()) A.sink = vec(a.sink, a.heads);
+        if (direct_q) {
+          A.direct_q = 1;
+          A.q_rank = 0;
+          A.o_q = in.add(a.q, (long long)a.heads * (a.dim + a.rot_dim));
+        } else {
+          A.o_dq = in.add(a.dq, a.q_rank);
+        }
         A.o_dkv = in.add(a.dkv, (long long)a.kv_rank + a.rot_dim);
-        A.o_g = in.add(a.g, (long long)a.heads * a.vdim);
-        A.q_norm = vec(a.dq_norm, a.q_rank);
+        if (a.g.empty()) A.no_gate = 1;
+        else A.o_g = in.add(a.g, (long long)a.heads * a.vdim);
+        if (!direct_q) {
+          A.q_norm = vec(a.dq_norm, a.q_rank);
+          A.w_uq = mat(a.uq, (long long)a.heads * (a.dim + a.rot_dim), a.q_rank);
+        }
         A.kv_norm = vec(a.dkv_norm, a.kv_rank);
-        A.w_uq = mat(a.uq, (long long)a.heads * (a.dim + a.rot_dim), a.q_rank);
         {
           // W_uk [heads * dim, kv_rank] -> per head its transpose [kv_rank, dim]: the matrix that carries a head's plain
           // query part into the latent space
@@ -448,9 +534,15 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         if (d.ff < 1) throw std::runtime_error("dense feed-forward: ff must be positive");
         L.dense.ff = d.ff;
         L.dense.act = d.act;
-        L.dense.o_gate = fin.add(d.gate, d.ff);
+        if (d.act != THA_ACT_RELU2 && d.act != THA_ACT_XIELU) L.dense.o_gate = fin.add(d.gate, d.ff);
         L.dense.o_up = fin.add(d.up, d.ff);
         L.dense.w_down = mat(d.down, W, d.ff);
+        if (d.act == THA_ACT_XIELU) {
+          std::vector<float> pq;
+          file.read_f32(d.act_params, &pq);
+          if (pq.size() != 2) throw std::runtime_error("tensor '" + d.act_params + "' must hold two numbers");
+          L.dense.act_p = pq[0]; L.dense.act_q = pq[1];
+        }
       } else if (ls.has_ff) {
         const MoeSpec& e = ls.moe;
         if (e.top < 1 || e.top > e.experts || e.top > 32) throw std::runtime_error("mixture of experts: 1 <= top <= min(experts, 32)");
@@ -485,6 +577,14 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
           if (!e.s_scale.empty()) { E.shared_scaled = 1; E.o_sscale = fin.add(e.s_scale, 1); }
         }
       }
+      if (ls.side.dim > 0) {
+        if (spec.side_table.empty() || ls.side.col0 < 0 || ls.side.col0 + ls.side.dim > spec.side_cols)
+          throw std::runtime_error("a layer's side input does not fit the side table");
+        L.side.dim = ls.side.dim; L.side.col0 = ls.side.col0;
+        L.side.w_gate = mat(ls.side.gate, ls.side.dim, W);
+        L.side.w_proj = mat(ls.side.proj, W, ls.side.dim);
+        L.side.norm = vec(ls.side.norm, W);
+      }
       L.n_in = in.rows;
       L.w_in = m->upload(in.data(), in.bytes());
       if (two) {
@@ -502,6 +602,12 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
     M.eps = spec.eps;
     M.logit_softcap = spec.logit_softcap;
     M.embed = mat(spec.embed, spec.vocab, W);
+    M.embed_scale = spec.embed_scale;
+    if (!spec.side_table.empty()) {
+      if (spec.side_cols < 1) throw std::runtime_error("a side table needs its number of columns");
+      M.side_table = mat(spec.side_table, spec.vocab, spec.side_cols);
+      M.side_cols = spec.side_cols;
+    }
     if (!spec.pos_embed.empty()) {
       if (spec.max_positions < 1) throw std::runtime_error("a position table needs max_positions");
       M.pos_embed = mat(spec.pos_embed, spec.max_positions, W);

@@ -20,6 +20,7 @@
 struct RotarySpec {
   int dims = 0;
   double base = 10000.0;
+  bool halves = false;        // pairs (i, i + dims / 2) instead of (2i, 2i + 1); the table is the same, the kernels pair by it
   bool yarn = false;          // frequency interpolation between a fast and a slow wavelength bound
   double factor = 1.0, original = 0.0, fast = 32.0, slow = 1.0;
   bool operator==(const RotarySpec& o) const {
@@ -33,6 +34,20 @@ struct AttnSpec {
   RotarySpec rot;
   float scale = 1.0f;
   std::string q, k, v, o;
+  int window = 0, keep_first = 0;        // window 0: every earlier position of the block of positions is seen
+  std::string sink;                      // [heads] a learned score in the softmax denominator; empty: none
+  bool sink_zero = false;                // a sink fixed at zero (a constant 1 in the normalising sum): no tensor
+  std::string temp;                      // [heads] per-head factor on the scores; empty: none
+  std::string g;                         // [heads, width] one sigmoid output gate per head; empty: none
+  bool fp32_scores = false;              // scores and softmax weights stay fp32 in every number format
+};
+struct GDeltaSpec {
+  int heads = 0, dim = 0;
+  std::string r, k, v, g, a, a_b, w1, w2, w0, norm, o;   // the rank of w1 / w2 is read from the tensors
+};
+struct SideSpec {
+  int dim = 0, col0 = 0;                 // dim 0: none
+  std::string gate, proj, norm;
 };
 struct MemSpec {
   int heads = 0, dim = 0, vdim = 0;
@@ -54,10 +69,15 @@ struct LatentSpec {
   RotarySpec rot;
   float scale = 1.0f;
   std::string dq, dq_norm, uq, dkv, dkv_norm, uk, uv, g, o;
+  std::string q;                         // queries straight from the layer input [heads * (dim + rot_dim), width]: no query latent
+  int window = 0;                        // > 0: sliding window
+  std::string sink;                      // [heads]; empty: none
+  bool fp32_scores = false;
 };
 struct DenseSpec {
   int ff = 0, act = THA_ACT_GELU_TANH_GLU;
-  std::string gate, up, down;
+  std::string gate, up, down;            // ungated activations have no `gate`
+  std::string act_params;                // THA_ACT_XIELU: [2]
 };
 struct MoeSpec {
   int experts = 0, top = 0, ff = 0, shared_ff = 0;
@@ -85,6 +105,14 @@ struct LayerSpec {
   MemSpec mem;
   std::string left_out, right_out;
   DeltaSpec delta;
+  int block = THA_BLOCK_PARALLEL;
+  float res_mult = 1.0f;                 // sequential blocks
+  GDeltaSpec gdelta;                     // THA_MIX_ATTN_GDELTA (beside attn)
+  float mix_left = 1.0f, mix_right = 1.0f;
+  SideSpec side;
+  bool pre_add_embed = false;            // before this run: x += the embedding output
+  std::string pre_vec;                   // before this run: x += row pre_vec_row of this [rows, width] tensor; empty: none
+  int pre_vec_row = 0;
   bool has_ff = false;
   MoeSpec moe;
 };
@@ -94,6 +122,9 @@ struct LayerProgramSpec {
   // every norm over the width (the layers' and the final one): THA_NORM_RMS with weights stored around zero, or
   // THA_NORM_DYT with "<name>.alpha" (a scalar) and "<name>.b" beside the weight
   int norm_kind = THA_NORM_RMS;
+  float embed_scale = 1.0f;
+  std::string side_table;                // [vocab, side_cols]: per-token side inputs, a column range per layer; empty: none
+  int side_cols = 0;
   std::string pos_embed;                 // learned position vectors [max_positions, width]; empty: none
   int max_positions = 0;                 // 0: no limit from the model
   std::string embed, final_norm, head;

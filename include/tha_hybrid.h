@@ -34,9 +34,15 @@ extern "C" {
 #define THA_MIX_DELTA 1    /* gated delta rule with per-channel decay */
 #define THA_MIX_GLA 2      /* gated linear attention: decayed outer-product memory, decay per key channel */
 #define THA_MIX_LATENT 3   /* softmax attention whose keys and values are expanded from one cached low-rank latent */
+#define THA_MIX_ATTN 4     /* softmax attention alone (tha_attn_t with its window, sink, per-head scale and gate options) */
+#define THA_MIX_ATTN_GDELTA 5 /* softmax attention and a generalized delta rule side by side: mix_left * left + mix_right * right */
+
+#define THA_BLOCK_PARALLEL 0   /* x <- x + mixer(norm1 x) + ff(norm x): mixer and feed-forward read the same x */
+#define THA_BLOCK_SEQUENTIAL 1 /* x <- x + m mixer(norm1 x), then x <- x + m ff(norm2 x), then the per-token side input */
 
 #define THA_NORM_RMS 0     /* x / sqrt(mean(x^2) + eps) * (w_offset + w) */
 #define THA_NORM_DYT 1     /* tanh(alpha * x) * w + b: element-wise, no statistics */
+#define THA_NORM_LAYER 2   /* (x - mean) / sqrt(variance + eps) * w + b, variance = mean of the squared deviations */
 
 #define THA_FF_NONE 0
 #define THA_FF_MOE 1
@@ -45,6 +51,7 @@ extern "C" {
 #define THA_ACT_GLU_CLAMPED 0 /* g' = min(g, limit), u' = clamp(u, +-limit): g' sigmoid(alpha g') (u' + 1) */
 #define THA_ACT_RELU2 1       /* max(u, 0)^2, no gate */
 #define THA_ACT_GELU_TANH_GLU 2 /* gelu(g) u, gelu in its tanh form */
+#define THA_ACT_XIELU 3       /* no gate; z > 0: softplus(p) z^2 + z / 2; z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z / 2 */
 
 #define THA_ROUTE_TOPK_SOFTMAX 0    /* the top logits, softmax over the chosen */
 #define THA_ROUTE_SOFTMAX_GROUPS 1  /* softmax over all experts; choice by score + correction inside the best groups of
@@ -52,6 +59,9 @@ extern "C" {
 
 #define THA_GATE_SIGMOID 0
 #define THA_GATE_SILU 1
+
+#define THA_ROT_INTERLEAVED 0 /* rotary pairs (2i, 2i + 1) */
+#define THA_ROT_HALVES 1      /* rotary pairs (i, i + dims / 2) */
 
 /* The rows of one step.  Rows of a sequence are consecutive and in ascending position. */
 typedef struct {
@@ -93,13 +103,17 @@ typedef struct {
 typedef struct {
   int kind;          /* THA_NORM_* */
   const float* w;    /* [width] */
-  const float* b;    /* [width], THA_NORM_DYT */
+  const float* b;    /* [width], THA_NORM_DYT and THA_NORM_LAYER */
   float w_offset;    /* THA_NORM_RMS: 1 when the weight is stored around zero */
   float alpha;       /* THA_NORM_DYT */
 } tha_norm_t;
 
 /* Softmax attention over the cache.  A query at position p sees the keys j <= p with
- * floor(j / chunk) == floor(p / chunk) when chunk > 0, every j <= p otherwise. */
+ * floor(j / chunk) == floor(p / chunk) when chunk > 0, every j <= p otherwise; with window > 0 only those of them with
+ * p - j < window or j < keep_first (nothing is renumbered: rotation and distances use absolute positions).
+ * sink (per head): one more term exp(sink[h]) in the softmax's normalising sum; it brings no value and is not scaled.
+ * head_scale (per head): the scores of head h are multiplied by head_scale[h] on top of `scale`.
+ * Output gate per head: head h's result is multiplied by sigmoid of column o_g + h of the stacked projection. */
 typedef struct {
   int heads, kv_heads, dim, vdim;
   int rot;          /* index into the model's rotary tables, -1: none */
@@ -112,7 +126,32 @@ typedef struct {
   const void* w_o;  /* [width, heads * vdim] */
   int values_in_keys; /* 1: a value row is the first vdim channels of its key row (vdim <= dim): callers pass the K pool as
                          v_pool as well, and kernels may stage one tile for both */
+  /* zero-initialised, the fields below keep the behaviour described so far */
+  int window, keep_first;  /* window 0: no window */
+  const float* sink;       /* [heads], NULL: none */
+  const float* head_scale; /* [heads], NULL: none */
+  int rot_layout;          /* THA_ROT_* */
+  int head_gate, o_g;      /* head_gate 1: `heads` gate columns at o_g; tha_hyb_attn_gated applies them */
+  int fp32_scores;         /* 1: scores and softmax weights stay fp32 in every number format (no bf16 rounding of q, k or weights) */
 } tha_attn_t;
+
+/* Generalized delta rule with a decay and a removal rate per key channel.  r, k, v, g: heads x dim columns each.
+ *   decay   w = exp(-exp(-1/2) * sigmoid(W_w2 tanh(W_w1 h) + w0))      removal rate   a = sigmoid(W_a h + a_b)
+ *   unit key u = k / sqrt(sum(k^2) + 1e-6) per head
+ *   S_t = diag(w) S_(t-1) - (a * u) (u^T S_(t-1)) + k v^T  (S on the right: the state before the token, throughout),   o_t = S_t^T r
+ * The read-out is divided by its root mean square per head, weighted (norm, [heads * dim]) and gated by sigmoid(g).
+ * State per head: dim x dim floats laid out for the scan ([column pair][key channel][2], an odd last column padded). */
+typedef struct {
+  int heads, dim, rank;
+  float eps;
+  int o_r, o_k, o_v, o_g, o_a, o_w1; /* columns of the stacked input projection (w1: rank columns) */
+  const void* w_w2;     /* [heads * dim, rank] */
+  const float* w0;      /* [heads * dim] */
+  const float* a_b;     /* [heads * dim] */
+  const float* norm;    /* [heads * dim] */
+  const void* w_o;      /* [width, heads * dim] */
+  long long state_off;
+} tha_gdelta_t;
 
 /* Matrix memory with exponential input gate, sigmoid forget gate (both in log space, soft-capped) and a running
  * maximum that starts at 0.  State per head: S [dim, vdim], n [dim], m. */
@@ -178,14 +217,31 @@ typedef struct {
   const void* w_uk_t;   /* [heads][kv_rank, dim]: W_uk of each head, transposed */
   const void* w_uv;     /* [heads][vdim, kv_rank] */
   const void* w_o;      /* [width, heads * vdim] */
+  /* zero-initialised, the fields below keep the behaviour described above */
+  int direct_q, o_q;    /* direct_q 1: no query latent; q = heads * (dim + rot_dim) columns at o_q of the stacked projection */
+  int no_gate;          /* 1: no output gate */
+  int window;           /* > 0: a query at p sees the keys j with 0 <= p - j < window */
+  const float* sink;    /* [heads], NULL: none (see tha_attn_t) */
+  int rot_layout;       /* THA_ROT_* */
+  int fp32_scores;      /* see tha_attn_t */
 } tha_latent_t;
 
 /* Dense gated feed-forward: W_down act(W_gate h, W_up h). */
 typedef struct {
   int ff, act;
-  int o_gate, o_up;     /* columns of the feed-forward's stacked input projection */
+  int o_gate, o_up;     /* columns of the feed-forward's stacked input projection (ungated activations: o_up only) */
   const void* w_down;   /* [width, ff] */
+  float act_p, act_q;   /* THA_ACT_XIELU: the two stored numbers (softplus is taken by the kernel) */
 } tha_dense_ff_t;
+
+/* Per-token side input of a layer, after its feed-forward: e = table[token, col0 : col0 + dim];
+ * y = W_proj (gelu_tanh(W_gate x) * e); x <- x + m * y / sqrt(mean(y^2) + eps) * norm. */
+typedef struct {
+  int dim, col0;        /* dim 0: the layer has none */
+  const void* w_gate;   /* [dim, width] */
+  const void* w_proj;   /* [width, dim] */
+  const float* norm;    /* [width] */
+} tha_side_t;
 
 /* Mixture of experts with clamped gated activation: g = min(gate, limit), u = clamp(up, -limit, limit),
  * y = g * sigmoid(alpha * g) * (u + 1).  Router: top-k logits, softmax over the chosen.  Optional shared expert. */
@@ -231,6 +287,15 @@ typedef struct {
   int has_ff;           /* THA_FF_* */
   tha_moe_t moe;        /* THA_FF_MOE */
   tha_dense_ff_t dense; /* THA_FF_DENSE */
+  /* zero-initialised, the fields below keep the behaviour described above */
+  int block;            /* THA_BLOCK_*; sequential blocks: dense or no feed-forward, reading norm2 through w_in2 */
+  float res_mult;       /* THA_BLOCK_SEQUENTIAL: m */
+  tha_gdelta_t gdelta;  /* THA_MIX_ATTN_GDELTA (beside attn) */
+  float mix_left, mix_right; /* THA_MIX_ATTN_GDELTA */
+  tha_side_t side;
+  /* before this run's first norm: x += the embedding output (pre_add_embed), then x += pre_vec ([width], NULL: none) */
+  int pre_add_embed;
+  const float* pre_vec;
 } tha_hyb_layer_t;
 
 typedef struct {
@@ -248,6 +313,9 @@ typedef struct {
   const tha_hyb_layer_t* layers;
   int n_rot;
   const tha_rotary_t* rot;       /* host array */
+  float embed_scale;             /* the embedding rows are multiplied by it; 0 reads as 1 */
+  const void* side_table;        /* [vocab, side_cols]: the per-token side inputs of all layers, NULL: none */
+  int side_cols;
 } tha_hyb_model_t;
 
 /* One scheduler step: every row through every layer; logits [n_want, vocab] (fp32) of the rows listed in want_rows.
@@ -282,6 +350,24 @@ int tha_hyb_rotary_table(void* stream, const tha_rotary_t* rot, const int* pos, 
 /* rotate q and k, unit-rms them, write k and v to the cache rows of (slot, pos), q to q_out [n_rows, heads * dim] */
 int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* proj,
                          long long ldp, const float* cos_t, const float* sin_t, int rot_dims, float* q_out);
+/* tha_hyb_attn with the per-head output gate of a.head_gate read from proj (columns a.o_g ..); proj NULL: no gate */
+int tha_hyb_attn_gated(void* stream, int dtype, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* q,
+                       void* out, float* split_scratch, size_t split_scratch_floats, const float* proj, long long ldp);
+/* the generalized delta rule over the rows of every sequence in order: the w1 columns of proj are replaced by their tanh,
+ * w_raw [n_rows, heads * dim] receives W_w2 tanh(.) and then the decays, the a columns of proj become the removal rates;
+ * the read-out goes to o_raw (fp32 [n_rows, heads * dim]) and, normed and gated, to out (dtype-typed) */
+int tha_hyb_gdelta_scan(void* stream, int dtype, const tha_gdelta_t* g, const tha_rows_t* rows, const tha_state_store_t* st,
+                        float* proj, long long ldp, float* w_raw, float* o_raw, void* out);
+/* floats of one sequence's state of a generalized-delta-rule layer */
+long long tha_hyb_gdelta_state_floats(int heads, int dim);
+/* the end of a sequential block: x += m * ff (ff NULL: none), then the side input of tha_side_t (side->dim 0: none);
+ * tap (nullable) receives x */
+int tha_hyb_side_finish(void* stream, int dtype, float* x, const float* ff, float m, const tha_side_t* side, const void* side_table,
+                        int side_cols, const int* token, float eps, int n_rows, int width, float* tap);
+/* x += c_left * left + c_right * right (right NULL: none) (+ embed_out when given) (+ vec when given); then, with n not NULL,
+ * out (dtype-typed) = the norm n of x.  left NULL: only the optional addends. */
+int tha_hyb_add_norm(void* stream, int dtype, float* x, const float* left, float c_left, const float* right, float c_right,
+                     const float* embed_out, const float* vec, const tha_norm_t* n, float eps, void* out, int n_rows, int width);
 /* softmax attention of every row over its visible cache rows; out dtype-typed [n_rows, heads * vdim].
  * split_scratch (nullable, fp32): room for the partial results when a step of few rows at long contexts is cut along
  * the keys (splits * n_rows * heads * (vdim + 2) floats are used, as many splits as fit, at most 16) */
@@ -308,12 +394,12 @@ int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_
  * the following rot_dim columns, rotated] */
 int tha_hyb_latent_prepare(void* stream, int dtype, const tha_latent_t* a, const tha_rows_t* rows, const tha_kv_t* kv,
                            const float* proj, long long ldp, const float* cos_t, const float* sin_t, int rot_dims, void* cq);
-/* latent attention, after the query expansion qfull fp32 [n_rows, heads * (dim + rot_dim)]: the plain parts go to
- * q_plain (dtype-typed [n_rows, heads * dim]), the rotated parts to columns kv_rank.. of q_abs (fp32 [n_rows, heads *
- * (kv_rank + rot_dim)]) whose first kv_rank columns per head the caller fills with W_uk^T q_plain */
-int tha_hyb_latent_split_q(void* stream, int dtype, const tha_latent_t* a, int n_rows, const float* qfull, const float* cos_t,
-                           const float* sin_t, int rot_dims, void* q_plain, float* q_abs);
-/* out (dtype-typed [n_rows, heads * E]) = o_raw * gate_act(gate), with do_norm: o_raw divided by its rms per head and
+/* latent attention, after the query expansion qfull fp32 (row pitch ldq floats; 0: heads * (dim + rot_dim)): the plain
+ * parts go to q_plain (dtype-typed [n_rows, heads * dim]), the rotated parts to columns kv_rank.. of q_abs (fp32 [n_rows,
+ * heads * (kv_rank + rot_dim)]) whose first kv_rank columns per head the caller fills with W_uk^T q_plain */
+int tha_hyb_latent_split_q(void* stream, int dtype, const tha_latent_t* a, int n_rows, const float* qfull, long long ldq,
+                           const float* cos_t, const float* sin_t, int rot_dims, void* q_plain, float* q_abs);
+/* out (dtype-typed [n_rows, heads * E]) = o_raw * gate_act(gate) (gate NULL: no gate), with do_norm: o_raw divided by its rms per head and
  * weighted by norm ([E], or [heads * E] with norm_per_head) first */
 int tha_hyb_head_gate(void* stream, int dtype, void* out, const float* o_raw, int n_rows, int heads, int E, int do_norm,
                       float eps, const float* norm, int norm_per_head, const float* gate, long long ldg, int gate_act);
@@ -328,7 +414,8 @@ int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* proj, long 
 /* y = g * sigmoid(alpha g) * (u + 1) with the clamps; gu [n, ldg] holds gate at col_g and up at col_u; y dtype-typed [n, ff] */
 int tha_hyb_glu_clamped(void* stream, int dtype, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
                         int ff, float limit, float alpha);
-/* the same for any THA_ACT_* (ungated activations read col_u only) */
+/* the same for any THA_ACT_* (ungated activations read col_u only; THA_ACT_XIELU takes its two stored numbers p, q as
+ * (limit, alpha)) */
 int tha_hyb_ff_act(void* stream, int dtype, int act, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
                    int ff, float limit, float alpha);
 
