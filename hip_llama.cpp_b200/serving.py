@@ -305,3 +305,79 @@ def random_numizen_tensors(cfg: dict, seed: int = 0, decay_rank: int = 64) -> di
             a = 1.0 + 0.2 * rng.standard_normal(shape)
         out[name] = np.asarray(a, dtype=np.float32)
     return out
+
+
+def bozovik_tensor_shapes(cfg: dict, decay_rank: int = 16) -> dict:
+    """name -> shape of every tensor a Bozovik config asks for (decay_rank: rows of the delta rule's first decay
+    projection, a property of the tensors and not of the config)."""
+    W, V = cfg["width"], cfg["vocab"]
+    s = {"embed": (V, W), "head": (V, W)}
+
+    def norm(n):
+        s[n], s[n + ".b"] = (W,), (W,)
+
+    def attention(q, m, windowed):
+        H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        s[q + "q"], s[q + "k"], s[q + "v"] = (H * D, W), (G * D, W), (G * E, W)
+        s[q + "g"], s[q + "o"] = (H, W), (W, H * E)
+        s[q + ("sink" if windowed else "temp")] = (H,)
+
+    norm("final.norm")
+    lp = cfg.get("loop")
+    if lp:
+        s["loop.step"] = (lp["times"], W)
+    side = cfg.get("token_side")
+    if side:
+        s["side.embed"] = (V, side["dim"] * len(cfg["layers"]))
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        norm(p + "norm1")
+        q = p + "mix."
+        if L["type"] == "attention":
+            attention(q, m, False)
+        elif L["type"] == "latent_attention":
+            H, D, R, E, K = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            s[q + "q"], s[q + "dkv"], s[q + "dkv.norm"] = (H * (D + R), W), (K + R, W), (K,)
+            s[q + "uk"], s[q + "uv"], s[q + "sink"], s[q + "o"] = (H * D, K), (H * E, K), (H,), (W, H * E)
+        else:
+            attention(q + "left.", m["left"], True)
+            r, q = m["right"], q + "right."
+            HD = r["heads"] * r["dim"]
+            for n in ("r", "k", "v", "g", "a"):
+                s[q + n] = (HD, W)
+            s[q + "a.b"] = s[q + "w0"] = s[q + "norm"] = (HD,)
+            s[q + "w1"], s[q + "w2"], s[q + "o"] = (decay_rank, W), (HD, decay_rank), (W, HD)
+        f = L.get("mlp")
+        if f:
+            norm(p + "norm2")
+            s[p + "mlp.up"], s[p + "mlp.down"], s[p + "mlp.act"] = (f["ff"], W), (W, f["ff"]), (2,)
+        if side:
+            s[p + "side.gate"], s[p + "side.proj"], s[p + "side.norm"] = (side["dim"], W), (W, side["dim"]), (W,)
+    return s
+
+
+def random_bozovik_tensors(cfg: dict, seed: int = 0, decay_rank: int = 16) -> dict:
+    """Random weights of a Bozovik config: matrices N(0, 1/in), norm weights around one with small biases, sinks and
+    head factors of order one, decay and removal biases where the memory neither freezes nor forgets at once."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape in bozovik_tensor_shapes(cfg, decay_rank).items():
+        last = name.rsplit(".", 1)[-1]
+        if last == "sink":
+            a = rng.standard_normal(shape)
+        elif last == "temp":
+            a = rng.uniform(0.7, 1.4, shape)
+        elif last == "act":
+            a = rng.standard_normal(shape) * 0.5
+        elif last == "w0":
+            a = rng.standard_normal(shape) - 1.0
+        elif last == "b":
+            a = 0.1 * rng.standard_normal(shape)
+        elif name == "loop.step":
+            a = 0.3 * rng.standard_normal(shape)
+        elif len(shape) == 2:
+            a = rng.standard_normal(shape, dtype=np.float32) * (1.0 if name in ("embed", "side.embed") else 1.0 / np.sqrt(shape[1]))
+        else:
+            a = 1.0 + 0.2 * rng.standard_normal(shape)
+        out[name] = np.asarray(a, dtype=np.float32)
+    return out

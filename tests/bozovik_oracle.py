@@ -233,3 +233,105 @@ class Stepper:
 
 def forward(cfg, W, tokens, taps=None):
     return Stepper(cfg, W).feed(tokens, taps)
+
+
+def embed(cfg, W, tokens):
+    return W["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
+
+
+# ---- random models ----------------------------------------------------------------------------------------------------
+def bf16_round(a):
+    a = np.asarray(a, dtype=np.float32)
+    u = a.view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) >> 16 << 16
+    return u.astype(np.uint32).view(np.float32).reshape(a.shape)
+
+
+def tensor_shapes(cfg, decay_rank=5):
+    """name -> shape of every tensor the design needs (the rank of the decay projection is a property of the tensors)"""
+    Wd, V = cfg["width"], cfg["vocab"]
+    s = {"embed": (V, Wd), "head": (V, Wd), "final.norm": (Wd,), "final.norm.b": (Wd,)}
+    if cfg.get("loop"):
+        s["loop.step"] = (cfg["loop"]["times"], Wd)
+    side = cfg.get("token_side")
+    if side:
+        s["side.embed"] = (V, side["dim"] * len(cfg["layers"]))
+    for i, L in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, L["mixer"]
+        s[p + "norm1"] = s[p + "norm1.b"] = (Wd,)
+        q = p + "mix."
+        sides = [(q, m, L["type"])] if L["type"] != "parallel" else [(q + "left.", m["left"], "left")]
+        for q2, a, kind in sides:
+            if kind == "latent_attention":
+                H, D, R, E, K = a["heads"], a["dim"], a["rot_dim"], a["vdim"], a["kv_rank"]
+                s[q2 + "q"], s[q2 + "dkv"], s[q2 + "dkv.norm"] = (H * (D + R), Wd), (K + R, Wd), (K,)
+                s[q2 + "uk"], s[q2 + "uv"], s[q2 + "sink"], s[q2 + "o"] = (H * D, K), (H * E, K), (H,), (Wd, H * E)
+            else:
+                H, G, D, E = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+                s[q2 + "q"], s[q2 + "k"], s[q2 + "v"] = (H * D, Wd), (G * D, Wd), (G * E, Wd)
+                s[q2 + "g"], s[q2 + "o"] = (H, Wd), (Wd, H * E)
+                s[q2 + ("temp" if kind == "attention" else "sink")] = (H,)
+        if L["type"] == "parallel":
+            r, q2 = m["right"], q + "right."
+            HD = r["heads"] * r["dim"]
+            for n in ("r", "k", "v", "g", "a"):
+                s[q2 + n] = (HD, Wd)
+            s[q2 + "a.b"] = s[q2 + "w0"] = s[q2 + "norm"] = (HD,)
+            s[q2 + "w1"], s[q2 + "w2"], s[q2 + "o"] = (decay_rank, Wd), (HD, decay_rank), (Wd, HD)
+        if L.get("mlp"):
+            s[p + "norm2"] = s[p + "norm2.b"] = (Wd,)
+            s[p + "mlp.up"], s[p + "mlp.down"], s[p + "mlp.act"] = (L["mlp"]["ff"], Wd), (Wd, L["mlp"]["ff"]), (2,)
+        if side:
+            s[p + "side.gate"], s[p + "side.proj"], s[p + "side.norm"] = (side["dim"], Wd), (Wd, side["dim"]), (Wd,)
+    return s
+
+
+def random_weights(cfg, seed=0, decay_rank=5):
+    """bf16-representable float64 weights, scaled so that activations stay of order one"""
+    rng = np.random.default_rng(seed)
+    W = {}
+    for name, shape in tensor_shapes(cfg, decay_rank).items():
+        last = name.rsplit(".", 1)[-1]
+        if last == "sink":
+            a = rng.standard_normal(shape)
+        elif last == "temp":
+            a = rng.uniform(0.6, 1.5, shape)
+        elif last == "act":
+            a = 0.5 * rng.standard_normal(shape)
+        elif last == "w0":
+            a = rng.standard_normal(shape) - 1.0
+        elif last == "b":
+            a = 0.1 * rng.standard_normal(shape)
+        elif name == "loop.step":
+            a = 0.3 * rng.standard_normal(shape)
+        elif len(shape) == 2 and name not in ("embed", "side.embed"):
+            a = rng.standard_normal(shape) / math.sqrt(shape[1])
+        elif len(shape) == 2:
+            a = rng.standard_normal(shape)
+        else:
+            a = 1.0 + 0.2 * rng.standard_normal(shape)
+        W[name] = bf16_round(a).astype(np.float64)
+    return W
+
+
+def self_check():
+    """the two statements agree with each other on a small model: whole prompt == portions == token by token"""
+    att = {"heads": 4, "kv_heads": 2, "dim": 6, "vdim": 5, "scale": 0.4, "rot": {"base": 100.0, "dims": 4}}
+    left = dict(att, mask={"size": 5, "keep_first": 2})
+    lat = {"heads": 2, "dim": 4, "rot_dim": 4, "vdim": 3, "kv_rank": 7, "scale": 0.35, "mask": {"size": 4}, "rot": {"base": 50.0, "dims": 4}}
+    cfg = {"architecture": "Bozovik", "width": 20, "vocab": 31, "norm": {"eps": 1e-5}, "residual_mult": 0.8, "embedding": {"scale": 2.0},
+           "token_side": {"dim": 3}, "loop": {"start": 1, "stop": 3, "times": 2},
+           "layers": [{"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": 12}},
+                      {"type": "parallel", "mixer": {"left": left, "right": {"heads": 2, "dim": 5}, "left_scale": 0.7, "right_scale": 1.2}, "mlp": None},
+                      {"type": "latent_attention", "mixer": lat, "mlp": {"kind": "dense", "ff": 9}}]}
+    W = random_weights(cfg, 3)
+    toks = np.random.default_rng(1).integers(0, 31, 19).tolist()
+    taps = []
+    z = forward(cfg, W, toks, taps)
+    assert len(taps) == 1 + 2 * 2
+    st = Stepper(cfg, W)
+    one = np.concatenate([st.feed([t]) for t in toks])
+    st = Stepper(cfg, W)
+    cut = np.concatenate([st.feed(toks[:7]), st.feed(toks[7:9]), st.feed(toks[9:])])
+    assert np.abs(one - z).max() < 1e-9 and np.abs(cut - z).max() < 1e-9
+    return True
