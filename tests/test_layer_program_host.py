@@ -8,6 +8,7 @@ import re
 import numpy as np
 import pytest
 
+import bozovik_oracle as B
 import numizen_oracle as N
 import timerax_oracle as O
 from pkgload import load_pkg
@@ -41,6 +42,7 @@ def test_registry_names_what_it_knows(tmp_path):
     with pytest.raises(serving.ServingError) as e:
         serving.ServingEngine(str(tmp_path), "float32", 64, 1)
     assert "Nope" in str(e.value) and "Timerax" in str(e.value) and "llama2" in str(e.value) and "Numizen" in str(e.value)
+    assert "Bozovik" in str(e.value)
 
 
 @built
@@ -199,3 +201,74 @@ def test_plain_rotation_pairs_neighbours():
     a0, a1 = 1.0, 10.0 ** -0.5                        # f_i = base^(-2i/dims)
     assert np.allclose(r[0, 0], 0 * np.cos(a0) - 1 * np.sin(a0)) and np.allclose(r[0, 1], 1 * np.cos(a0) + 0 * np.sin(a0))
     assert np.allclose(r[0, 2], 2 * np.cos(a1) - 3 * np.sin(a1)) and np.allclose(r[0, 4:], x[0, 4:])
+
+
+# ---- Bozovik ----------------------------------------------------------------------------------------------------------
+def _bozovik_cfg(layers, **extra):
+    c = {"architecture": "Bozovik", "width": 16, "vocab": 20, "norm": {"eps": 1e-5}, "residual_mult": 0.9, "embedding": {"scale": 2.0}, "layers": layers}
+    c.update(extra)
+    return c
+
+
+@built
+def test_bozovik_configs_are_refused_by_name(tmp_path):
+    serving = load_pkg("serving")
+    att = {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 4, "vdim": 4, "scale": 0.5}, "mlp": None}
+    no_scale = {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 4, "vdim": 4}, "mlp": None}
+    left = {"heads": 2, "kv_heads": 1, "dim": 4, "vdim": 4, "scale": 0.5, "mask": {"size": 0}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": {"heads": 1, "dim": 4}, "left_scale": 1.0, "right_scale": 1.0}, "mlp": None}
+    for cfg, word in [(_bozovik_cfg([{"type": "helix", "mixer": {}, "mlp": None}]), "helix"),
+                      (_bozovik_cfg([att], loop={"start": 0, "stop": 3, "times": 2}), "loop"),
+                      (_bozovik_cfg([dict(att, mlp={"kind": "sparse"})]), "sparse"),
+                      (_bozovik_cfg([no_scale]), "scale"),
+                      (_bozovik_cfg([par]), "window"),
+                      ({k: v for k, v in _bozovik_cfg([att]).items() if k != "residual_mult"}, "residual_mult")]:
+        (tmp_path / "config.json").write_text(json.dumps(cfg))
+        with pytest.raises(serving.ServingError) as e:
+            serving.ServingEngine(str(tmp_path), "float32", 64, 1)
+        assert word in str(e.value), (word, str(e.value))
+
+
+def test_bozovik_tensor_shapes_cover_a_config():
+    serving = load_pkg("serving")
+    lat = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": 12},
+           "mixer": {"heads": 2, "dim": 4, "rot_dim": 2, "vdim": 6, "kv_rank": 10, "scale": 0.4, "mask": {"size": 5}, "rot": {"base": 100.0, "dims": 2}}}
+    left = {"heads": 2, "kv_heads": 1, "dim": 4, "vdim": 6, "scale": 0.5, "mask": {"size": 3, "keep_first": 1}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": {"heads": 3, "dim": 5}, "left_scale": 1.0, "right_scale": 1.0}, "mlp": None}
+    cfg = _bozovik_cfg([lat, par], token_side={"dim": 3}, loop={"start": 0, "stop": 1, "times": 4})
+    t = serving.random_bozovik_tensors(cfg, 0, decay_rank=7)
+    assert t["l0.mix.q"].shape == (12, 16) and t["l0.mix.dkv"].shape == (12, 16) and t["l0.mix.sink"].shape == (2,)
+    assert t["l1.mix.left.g"].shape == (2, 16) and t["l1.mix.right.w2"].shape == (15, 7) and t["l1.mix.right.a.b"].shape == (15,)
+    assert t["side.embed"].shape == (20, 6) and t["loop.step"].shape == (4, 16) and "l1.mlp.up" not in t and "l1.norm2" not in t
+    assert set(t) == set(B.tensor_shapes(cfg, 7))
+
+
+def test_plain_bozovik_statements_agree():
+    assert B.self_check()
+
+
+def test_plain_bozovik_masks_sinks_and_rotation():
+    vis = B.visible([0, 5, 9], 10, window=3, keep_first=2)
+    assert vis[0].tolist() == [True] + [False] * 9
+    assert vis[1].tolist() == [True, True, False, True, True, True, False, False, False, False]
+    assert vis[2].tolist() == [True, True, False, False, False, False, False, True, True, True]
+    s = np.zeros((1, 1, 4))
+    w = B.sink_softmax(s, np.array([[True, True, False, True]]), np.array([0.0]))
+    assert np.allclose(w[0, 0], [0.25, 0.25, 0.0, 0.25])           # the sink takes a quarter and gives nothing back
+    x = np.arange(6, dtype=np.float64)[None, :]
+    r = B.rotate_half(x, [1], 4, 1.0)                                # pairs (0, 2) and (1, 3); entries 4 and 5 pass
+    assert np.allclose(r[0, 4:], [4.0, 5.0])
+    assert np.allclose(r[0, 0], 0.0 * np.cos(1.0) - 2.0 * np.sin(1.0)) and np.allclose(r[0, 2], 2.0 * np.cos(1.0) + 0.0 * np.sin(1.0))
+
+
+def test_plain_delta_rule_removes_along_the_unit_key():
+    """one head, a key repeated with full removal and no decay: the second write replaces what the first stored"""
+    D = 4
+    W = {"r": np.eye(D), "k": np.eye(D), "v": np.eye(D), "g": np.zeros((D, D)), "a": np.zeros((D, D)), "a.b": np.full(D, 40.0),
+         "w1": np.zeros((1, D)), "w2": np.zeros((D, 1)), "w0": np.full(D, -40.0), "norm": np.ones(D), "o": np.eye(D)}
+    W = {"p." + k: v for k, v in W.items()}
+    h = np.array([[2.0, 0, 0, 0], [2.0, 0, 0, 0]])
+    st = {}
+    B.delta_mixer(h, {"heads": 1, "dim": D}, W, "p.", 1e-6, st)
+    # after token 1: S = k v^T (4 at [0, 0]); token 2 removes u u^T S = all of it and writes k v^T again
+    assert np.allclose(st["S"][0], np.diag([4.0, 0, 0, 0]), atol=1e-5)
