@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);          // [PAIRS][DS]
   __nv_bfloat16* Ks = Qs + (size_t)PAIRS * DS;                             // [32][DS]
   __nv_bfloat16* Pb = Ks + (size_t)WK_KEYS * DS;                           // [PAIRS][40] weights
-  float* Sf = reinterpret_cast<float*>(Pb + PAIRS * 40);                   // [4][PAIRS][33] partial scores
+  __nv_bfloat16* Pl = Pb + PAIRS * 40;                                     // [PAIRS][40] what their rounding to bf16 left over
+  float* Sf = reinterpret_cast<float*>(Pl + PAIRS * 40);                   // [4][PAIRS][33] partial scores
   float* corr_s = Sf + 4 * PAIRS * 33;                                       // [PAIRS] rescale factors, then 1 / sum
   float* m_s = corr_s + PAIRS;                                             // [PAIRS] running maxima at the end
   int seq = -1, r0 = 0, r_end = 0;
@@ -146,16 +147,19 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
   for (int n = 0; n < WK_MAX_SLICE / 8; n++)
 #pragma unroll
     for (int v = 0; v < 4; v++) oacc[n][v] = 0.f;
-  int kt_begin = 0, kt_last = p_last;
+  const bool exact = a.fp32_scores != 0;
+  const HybTiles tiles = hyb_attn_tiles(a, 0, p_first, p_last);
+  int ti_begin = 0, ti_end = tiles.n;
   if (splits > 1) {
-    const int n_kt = p_last / WK_KEYS + 1, per = (n_kt + splits - 1) / splits, sp = blockIdx.x % splits;
-    kt_last = min(p_last, (sp + 1) * per * WK_KEYS - 1);
-    kt_begin = sp * per * WK_KEYS;
+    const int per = (tiles.n + splits - 1) / splits, sp = blockIdx.x % splits;
+    ti_begin = sp * per;
+    ti_end = min(tiles.n, ti_begin + per);
   }
   // cache rows start on 16-byte boundaries when the pool's row pitch and the head's offset are multiples of four floats
   const bool vec4 = (kv.kv_dim & 3) == 0 && (D & 3) == 0 && (reinterpret_cast<size_t>(kv.k_pool) & 15) == 0;
   const unsigned ks_base = (unsigned)__cvta_generic_to_shared(Ks), qs_base = (unsigned)__cvta_generic_to_shared(Qs);
-  for (int kt = kt_begin; kt <= kt_last; kt += WK_KEYS) {
+  for (int ti = ti_begin; ti < ti_end; ti++) {
+    const int kt = ti < tiles.n_a ? tiles.begin + WK_KEYS * ti : tiles.resume + WK_KEYS * (ti - tiles.n_a);
     __syncthreads();   // the previous tile's weights and values have been used (first pass: the queries are in place)
     // 1. the tile's key rows; keys past the last position of the block are zero
     for (int j = warp; j < WK_KEYS; j += NW) {
@@ -228,7 +232,7 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
 #pragma unroll
     for (int rr = 0; rr < 4; rr++) {
       const int pr = warp * 4 + rr, t = kt + lane;
-      const bool vis = s_ok[rr] && t <= s_pos[rr];
+      const bool vis = s_ok[rr] && hyb_attn_sees(a, t, s_pos[rr], 0);
       const float* sp = Sf + pr * 33 + lane;   // the four channel shares, summed in a fixed order
       const float sv = vis ? ((sp[0] + sp[PAIRS * 33]) + (sp[2 * PAIRS * 33] + sp[3 * PAIRS * 33])) * a.scale : -INFINITY;
       const float m_new = fmaxf(m_run[rr], warp_max(sv));
@@ -238,23 +242,32 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
         corr = expf(m_run[rr] - m_new);      // 0 when nothing was seen before
       }
       const __nv_bfloat16 pb = __float2bfloat16_rn(p);
-      l_run[rr] = l_run[rr] * corr + warp_sum(__bfloat162float(pb));
+      // exact: the sum adds the fp32 weights, and hi + lo (16 mantissa bits) meet the values; else the rounded weights do both
+      l_run[rr] = l_run[rr] * corr + warp_sum(exact ? p : __bfloat162float(pb));
       m_run[rr] = m_new;
       Pb[pr * 40 + lane] = pb;
+      if (exact) Pl[pr * 40 + lane] = __float2bfloat16_rn(p - __bfloat162float(pb));
       if (lane == 0) corr_s[pr] = corr;
     }
     __syncthreads();
     // 4. accumulators of row tile mi, channels ei * ES ..: rescale, then weights x values
     {
       const float ca = corr_s[mi * 16 + lr], cb = corr_s[mi * 16 + lr + 8];
-      uint32_t pf[2][4];
+      uint32_t pf[2][4], pg[2][4];
       const __nv_bfloat16* pa = Pb + (mi * 16 + lr) * 40 + lc;
+      const __nv_bfloat16* pc = Pl + (mi * 16 + lr) * 40 + lc;
 #pragma unroll
       for (int t2 = 0; t2 < 2; t2++) {
         pf[t2][0] = *reinterpret_cast<const uint32_t*>(pa + 16 * t2);
         pf[t2][1] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40 + 16 * t2);
         pf[t2][2] = *reinterpret_cast<const uint32_t*>(pa + 16 * t2 + 8);
         pf[t2][3] = *reinterpret_cast<const uint32_t*>(pa + 8 * 40 + 16 * t2 + 8);
+        if (exact) {
+          pg[t2][0] = *reinterpret_cast<const uint32_t*>(pc + 16 * t2);
+          pg[t2][1] = *reinterpret_cast<const uint32_t*>(pc + 8 * 40 + 16 * t2);
+          pg[t2][2] = *reinterpret_cast<const uint32_t*>(pc + 16 * t2 + 8);
+          pg[t2][3] = *reinterpret_cast<const uint32_t*>(pc + 8 * 40 + 16 * t2 + 8);
+        }
       }
 #pragma unroll
       for (int n = 0; n < WK_MAX_SLICE / 8; n += 2) {
@@ -274,6 +287,10 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
             const uint32_t v0[2] = {vf[0], vf[1]}, v1[2] = {vf[2], vf[3]};
             mma_bf16_m16n8k16(oacc[n], pf[t2], v0);
             if (two) mma_bf16_m16n8k16(oacc[n + 1], pf[t2], v1);
+            if (exact) {
+              mma_bf16_m16n8k16(oacc[n], pg[t2], v0);
+              if (two) mma_bf16_m16n8k16(oacc[n + 1], pg[t2], v1);
+            }
           }
         }
       }
@@ -300,7 +317,7 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
       if (ei == 0 && (lane & 3) == 0) { dst[E] = m_s[pr]; dst[E + 1] = l; }
       continue;
     }
-    const float inv = 1.0f / l;
+    const float inv = hyb_attn_final_factor(a, head, m_s[pr], l, nullptr);
     __nv_bfloat16* dst = out + (size_t)row * a.heads * E + (size_t)head * E + ei * ES;
 #pragma unroll
     for (int n = 0; n < WK_MAX_SLICE / 8; n++)
@@ -309,11 +326,11 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
 }
 
 static size_t wide_smem(const tha_attn_t* a, int pairs) {
-  return sizeof(__nv_bfloat16) * ((size_t)(pairs + WK_KEYS) * (a->dim + 8) + (size_t)pairs * 40) + sizeof(float) * ((size_t)4 * pairs * 33 + 2 * pairs);
+  return sizeof(__nv_bfloat16) * ((size_t)(pairs + WK_KEYS) * (a->dim + 8) + (size_t)2 * pairs * 40) + sizeof(float) * ((size_t)4 * pairs * 33 + 2 * pairs);
 }
 
 // one key/value head, key rows a multiple of 16 wide, values inside them, four slices of at most 128 channels that are multiples of 8, no
-// block-of-positions mask, and the larger block must fit shared memory
+// block-of-positions mask (a window and a sink are served; per-head factors and gates are not), and the larger block must fit shared memory
 bool hyb_attn_wide_ok(const tha_attn_t* a) {
   return a->values_in_keys && a->kv_heads == 1 && a->chunk == 0 && a->dim % 16 == 0 && a->vdim % 32 == 0 && a->vdim <= 4 * WK_MAX_SLICE && a->vdim <= a->dim &&
          (a->heads * a->vdim) % 2 == 0 && wide_smem(a, 64) <= 200 * 1024;

@@ -301,44 +301,6 @@ __global__ void hyb_attn_prepare_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t 
   }
 }
 
-// What the attention kernels share beyond the causal block-of-positions rule.
-// Visibility of key t for a query at p whose block of positions starts at `first`:
-__device__ __forceinline__ bool hyb_attn_sees(const tha_attn_t& a, int t, int p, int first) {
-  return t <= p && t >= first && (a.window <= 0 || p - t < a.window || t < a.keep_first);
-}
-// The key tiles (of 32, aligned to absolute multiples of 32) a block of queries at positions p_first..p_last walks: all from
-// the tile of key_lo to the tile of p_last, except, under a window, the run of tiles that lie wholly between the kept first
-// keys and the window of the block's first query.  Logical tile i of n: kt = i < n_a ? begin + 32 i : resume + 32 (i - n_a).
-struct HybTiles { int begin, n_a, resume, n; };
-__device__ __forceinline__ HybTiles hyb_attn_tiles(const tha_attn_t& a, int key_lo, int p_first, int p_last) {
-  HybTiles t;
-  t.begin = (key_lo / 32) * 32;
-  t.n_a = 0;
-  t.resume = t.begin;
-  if (a.window > 0) {
-    const int win_lo = max(key_lo, p_first - a.window + 1);
-    const int keep_end = min(a.keep_first, p_last + 1);                                  // kept keys: [key_lo, keep_end)
-    const int after_kept = keep_end > key_lo ? ((keep_end - 1) / 32 + 1) * 32 : t.begin;  // first tile past them
-    const int wt = (win_lo / 32) * 32;
-    if (wt > after_kept) { t.n_a = (after_kept - t.begin) / 32; t.resume = wt; }
-  }
-  t.n = t.n_a + (p_last - t.resume) / 32 + 1;
-  return t;
-}
-// The end of a (query, head): with m, l the running maximum and sum, the factor the accumulator is multiplied by --
-// 1 / (l + exp(sink - m)) in a form that cannot overflow, times the head's output gate.
-__device__ __forceinline__ float hyb_attn_final_factor(const tha_attn_t& a, int h, float m, float l, const float* gate_row) {
-  float f;
-  if (a.sink) {
-    const float sk = a.sink[h], M = fmaxf(m, sk), e = expf(m - M);
-    f = e / (l * e + expf(sk - M));
-  } else {
-    f = 1.0f / l;
-  }
-  if (gate_row) f *= hyb_sigmoid(gate_row[h]);
-  return f;
-}
-
 // ------------------------------------------------------------------------------------------------------------------
 // attention, prompts and decoding alike.  A block takes 16 (position, query head) pairs that share one key/value head:
 // AP consecutive positions of one sequence x AG heads of the group (AG = min(group size, 16), AP = 16 / AG), so a key
@@ -570,6 +532,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+template <bool EXACT>
 __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
                                                            __nv_bfloat16* __restrict__ out, int AG, int AP, int splits,
                                                            float* __restrict__ partial, const float* __restrict__ gate, long long ldg) {
@@ -694,7 +657,7 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
       }
     }
     // scale, mask, online softmax of rows A (values 0, 1 of every score tile) and B (values 2, 3)
-    uint32_t pa[2][4];
+    uint32_t pa[2][4], pl[2][4];   // the weights as A operands: rounded to bf16, and (EXACT) what the rounding left over
 #pragma unroll
     for (int x = 0; x < 2; x++) {
       float mx = -INFINITY;
@@ -718,7 +681,12 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
         float p0 = 0.f, p1 = 0.f;
         if (m_new > -INFINITY) { p0 = expf(sacc[j][2 * x] - m_new); p1 = expf(sacc[j][2 * x + 1] - m_new); }   // exp(-inf) = 0 for masked keys
         const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-        sum += __low2float(pr) + __high2float(pr);
+        if (EXACT) {   // hi + lo carry 16 mantissa bits of the fp32 weight; the sum adds the fp32 weights themselves
+          sum += p0 + p1;
+          pl[j >> 1][(j & 1) * 2 + x] = pack_bf16(p0 - __low2float(pr), p1 - __high2float(pr));
+        } else {
+          sum += __low2float(pr) + __high2float(pr);
+        }
         pa[j >> 1][(j & 1) * 2 + x] = *reinterpret_cast<const uint32_t*>(&pr);
       }
       sum += __shfl_xor_sync(THA_FULL_MASK, sum, 1);
@@ -739,6 +707,7 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
           b[0] = *reinterpret_cast<const uint32_t*>(vr);
           b[1] = *reinterpret_cast<const uint32_t*>(vr + 8);
           mma_bf16_16816(oacc[n], pa[t2], b);
+          if (EXACT) mma_bf16_16816(oacc[n], pl[t2], b);
         }
       }
     }
@@ -1546,14 +1515,12 @@ extern "C" int tha_hyb_attn_gated(void* stream, int dtype, const tha_attn_t* a, 
   if (a->window < 0 || a->keep_first < 0) return THA_STATUS_INVALID_ARG;
   const float* gate = (a->head_gate && proj) ? proj + a->o_g : nullptr;
   const long long ldg = ldp;
-  // what the wide form does not know: windows, sinks, per-head scales and gates
-  const bool plain = a->window == 0 && !a->sink && !a->head_scale && !gate;
   if (a->heads % a->kv_heads || a->vdim > 32 * ATT_MAX_VC) return THA_STATUS_NOT_SUPPORTED;
   const int gsize = a->heads / a->kv_heads;
   // bf16 with heads the tensor-core form covers: 64 pairs per block; else 16 pairs on the fp32 cores
-  const bool tc = dtype == THA_DT_BF16 && !a->fp32_scores && hyb_tc_linear() && hyb_tc_attn() && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= AM_MAXD && a->vdim <= AM_MAXD &&
+  const bool tc = dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= AM_MAXD && a->vdim <= AM_MAXD &&
                   (a->heads * a->vdim) % 2 == 0;
-  const bool wide = !tc && plain && !a->fp32_scores && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && hyb_attn_wide_ok(a);
+  const bool wide = !tc && !gate && !a->head_scale && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && hyb_attn_wide_ok(a);
   const int pairs = wide ? hyb_attn_wide_pairs(a, rows) : tc ? AM_PAIRS : ATT_PAIRS;
   const int AG = gsize < pairs ? gsize : pairs, AP = pairs / AG;
   const size_t smem = tc ? sizeof(__nv_bfloat16) * ((size_t)ATT_KEYS * (a->dim + 8) + (size_t)a->vdim * (ATT_KEYS + 8))
@@ -1580,7 +1547,10 @@ extern "C" int tha_hyb_attn_gated(void* stream, int dtype, const tha_attn_t* a, 
       const int st = hyb_attn_wide_launch(s, a, rows, kv, q, (bf16*)out, grid, pairs, AG, AP, splits, split_scratch);
       if (st != THA_STATUS_SUCCESS) return st;
     } else if (tc) {
-      THA_CUDA_OK(launch(hyb_attn_mma_kernel, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch, gate, ldg));
+      if (a->fp32_scores)
+        THA_CUDA_OK(launch(hyb_attn_mma_kernel<true>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch, gate, ldg));
+      else
+        THA_CUDA_OK(launch(hyb_attn_mma_kernel<false>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch, gate, ldg));
     } else {
       if (a->vdim <= 256) {
         if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_attn_kernel<bf16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

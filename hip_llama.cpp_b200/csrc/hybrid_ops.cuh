@@ -34,4 +34,41 @@ __device__ __forceinline__ size_t hyb_kv_row(const tha_kv_t& kv, int slot, int t
   const int blk = kv.table[(size_t)slot * kv.table_stride + t / kv.block_size];
   return ((size_t)blk * kv.n_cache_layers + layer) * kv.block_size * kv.kv_dim + (size_t)(t % kv.block_size) * kv.kv_dim;
 }
+// What the attention kernels share beyond the causal block-of-positions rule.
+// Visibility of key t for a query at p whose block of positions starts at `first`:
+__device__ __forceinline__ bool hyb_attn_sees(const tha_attn_t& a, int t, int p, int first) {
+  return t <= p && t >= first && (a.window <= 0 || p - t < a.window || t < a.keep_first);
+}
+// The key tiles (of 32, aligned to absolute multiples of 32) a block of queries at positions p_first..p_last walks: all from
+// the tile of key_lo to the tile of p_last, except, under a window, the run of tiles that lie wholly between the kept first
+// keys and the window of the block's first query.  Logical tile i of n: kt = i < n_a ? begin + 32 i : resume + 32 (i - n_a).
+struct HybTiles { int begin, n_a, resume, n; };
+__device__ __forceinline__ HybTiles hyb_attn_tiles(const tha_attn_t& a, int key_lo, int p_first, int p_last) {
+  HybTiles t;
+  t.begin = (key_lo / 32) * 32;
+  t.n_a = 0;
+  t.resume = t.begin;
+  if (a.window > 0) {
+    const int win_lo = max(key_lo, p_first - a.window + 1);
+    const int keep_end = min(a.keep_first, p_last + 1);                                  // kept keys: [key_lo, keep_end)
+    const int after_kept = keep_end > key_lo ? ((keep_end - 1) / 32 + 1) * 32 : t.begin;  // first tile past them
+    const int wt = (win_lo / 32) * 32;
+    if (wt > after_kept) { t.n_a = (after_kept - t.begin) / 32; t.resume = wt; }
+  }
+  t.n = t.n_a + (p_last - t.resume) / 32 + 1;
+  return t;
+}
+// The end of a (query, head): with m, l the running maximum and sum, the factor the accumulator is multiplied by --
+// 1 / (l + exp(sink - m)) in a form that cannot overflow, times the head's output gate.
+__device__ __forceinline__ float hyb_attn_final_factor(const tha_attn_t& a, int h, float m, float l, const float* gate_row) {
+  float f;
+  if (a.sink) {
+    const float sk = a.sink[h], M = fmaxf(m, sk), e = expf(m - M);
+    f = e / (l * e + expf(sk - M));
+  } else {
+    f = 1.0f / l;
+  }
+  if (gate_row) f *= hyb_sigmoid(gate_row[h]);
+  return f;
+}
 }  // namespace tha

@@ -132,7 +132,9 @@ typedef struct {
   const float* head_scale; /* [heads], NULL: none */
   int rot_layout;          /* THA_ROT_* */
   int head_gate, o_g;      /* head_gate 1: `heads` gate columns at o_g; tha_hyb_attn_gated applies them */
-  int fp32_scores;         /* 1: scores and softmax weights stay fp32 in every number format (no bf16 rounding of q, k or weights) */
+  int fp32_scores;         /* 1: softmax weights are never rounded to bf16.  The tensor-core forms then multiply them with the
+                              values as a bf16 pair hi + lo (16 mantissa bits) and sum the fp32 weights themselves; scores
+                              accumulate in fp32 in every form */
 } tha_attn_t;
 
 /* Generalized delta rule with a decay and a removal rate per key channel.  r, k, v, g: heads x dim columns each.

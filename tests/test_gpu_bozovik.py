@@ -453,6 +453,41 @@ def test_a_sink_takes_its_share(tmp_path):
         assert rel_err(feed(b.engine(), "a", toks, [20, 1]), z) < F32_TOL
 
 
+# ---- the tensor-core attention forms of the bfloat16 number format ------------------------------------------------------
+@pytest.mark.parametrize("kind", ["attention", "left", "latent", "wide_latent"])
+@pytest.mark.parametrize("cuts", [[300], [150, 86, 2, 1], [64, 1]])
+def test_tensor_core_attention_bfloat16_every_position(tmp_path, kind, cuts):
+    """Heads of 16 .. 128 channels (multiples of 16 / 8) take, in bfloat16, the form that keeps a warp's pairs in registers;
+    a cached latent row wider than 128 channels the form in which a block of warps shares the query rows and the output.
+    Both know the window, the kept first tokens, the sink, the head factors and the gates.  Peaked scores and a check of EVERY
+    position by itself: a key too many or too few, or a tile of keys lost, is an error of tens of percent there."""
+    if kind == "attention":
+        layer = attention(None, heads=4, kv_heads=2, dim=32, vdim=24, rot_dims=16, scale=0.7)
+    elif kind == "left":
+        layer = parallel(None, left=attn(heads=6, kv_heads=2, dim=48, vdim=64, rot_dims=48, scale=0.6, mask=(70, 3)), left_scale=1.0, right_scale=0.0)
+    elif kind == "latent":
+        layer = latent(None, heads=4, dim=24, rot_dim=16, vdim=16, kv_rank=48, window=70, scale=0.5)
+    else:
+        layer = latent(None, heads=4, dim=24, rot_dim=32, vdim=16, kv_rank=160, window=70, scale=0.5)
+    b = Built(tmp_path, model([layer], width=64, vocab=200, side=0, mult=1.0), 41)
+    n = 300
+    toks = tokens_for(b, n, 3)
+    _, layers = b.ref(toks)
+    base = O.embed(b.cfg, b.w, toks)
+    mix = layers[0] - base
+    e = b.engine("bfloat16")
+    at, got, i = 0, [], 0
+    while at < n:
+        c = min(cuts[min(i, len(cuts) - 1)], n - at)
+        got.append(e.step([("a", toks[at:at + c], [])], taps=True)[1][0])
+        at += c
+        i += 1
+    got = np.concatenate(got, 0) - base
+    worst = max(rel_err(got[p], mix[p]) for p in range(n))
+    assert worst < 6e-2, worst
+    assert rel_err(got, mix) < 2e-2
+
+
 # ---- other sizes: values that are often equal, or 1 ------------------------------------------------------------------
 @pytest.mark.parametrize("case", ["single", "wide_heads", "everything_small", "loop_all_twice", "loop_nothing", "loop_once", "odd_sizes", "plain",
                                   "window_one", "window_beyond"])
