@@ -1,6 +1,8 @@
 """Throughput of a layer-program design beside the llama2 bf16 path at equal size (bench.py --design timerax), or of
 Numizen beside Timerax -- the closest design the framework has: attention + a recurrent mixer + a mixture of experts --
-and llama2 at equal size (bench.py --design numizen).
+and llama2 at equal size (bench.py --design numizen); or of Bozovik beside Numizen with dense feed-forwards -- the closest
+design the framework has: latent attention + a recurrent mixer + a looped segment -- and llama2 at equal size (bench.py
+--design bozovik).
 
 Random weights at sizes that resemble a real model's layers; a few layers only, so that building the folder stays
 short.  For every size: prompt ingestion (one prompt in one step) and batched decoding (one token per live request per
@@ -51,7 +53,7 @@ NUMIZEN = {
 }
 
 
-def numizen_config(s: dict, n: dict, max_positions: int = 8192) -> dict:
+def numizen_config(s: dict, n: dict, max_positions: int = 8192, dense_everywhere: bool = False) -> dict:
     lat = {"heads": n["heads"], "dim": n["dim"], "rot_dim": n["rot_dim"], "vdim": n["vdim"], "q_rank": n["q_rank"], "kv_rank": n["kv_rank"],
            "scale": (n["dim"] + n["rot_dim"]) ** -0.5, "rot": {"base": 500000.0, "dims": n["rot_dim"]}}
     gl = {"heads": n["gheads"], "dim": n["gdim"], "vdim": n["gvdim"], "tau": 16.0}
@@ -60,10 +62,34 @@ def numizen_config(s: dict, n: dict, max_positions: int = 8192) -> dict:
     dense = {"kind": "dense", "ff": s["top"] * s["ff"] + s["sff"]}
     layers = []
     for i in range(s["layers"]):
-        mlp = dense if i == 0 else moe
+        mlp = dense if i == 0 or dense_everywhere else moe
         layers.append({"type": "gla", "mixer": gl, "mlp": mlp} if i % 4 == 2 else {"type": "latent_attention", "mixer": lat, "mlp": mlp})
     return {"architecture": "Numizen", "layers": layers, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"],
             "max_positions": max_positions}
+
+
+# Bozovik at the same widths and vocabulary: softmax attention with grouped heads, latent attention under a sliding window
+# ("w1024": cached row 96 + 32; "w2048": the full-size latent of 512 + 64), attention beside a generalized delta rule, and
+# attention again; layers 1 and 2 are a looped segment that runs once (so the pass vector is added); an ungated feed-forward
+# with as many weights as the gated one of the other arms (1.5 x its hidden size); a per-token side input.
+BOZOVIK = {
+    "w1024": dict(lheads=8, ldim=64, rot_dim=32, lvdim=64, kv_rank=96, window=1024, keep=4, dheads=8, ddim=64, side=64),
+    "w2048": dict(lheads=16, ldim=128, rot_dim=64, lvdim=128, kv_rank=512, window=2048, keep=4, dheads=16, ddim=128, side=128),
+}
+
+
+def bozovik_config(s: dict, n: dict) -> dict:
+    rot = {"base": 500000.0, "dims": s["dim"]}
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5, "rot": rot}
+    left = dict(att, mask={"size": n["window"], "keep_first": n["keep"]})
+    lat = {"heads": n["lheads"], "dim": n["ldim"], "rot_dim": n["rot_dim"], "vdim": n["lvdim"], "kv_rank": n["kv_rank"],
+           "scale": (n["ldim"] + n["rot_dim"]) ** -0.5, "mask": {"size": n["window"]}, "rot": {"base": 500000.0, "dims": n["rot_dim"]}}
+    mlp = {"kind": "dense", "ff": (s["top"] * s["ff"] + s["sff"]) * 3 // 2}
+    par = {"left": left, "right": {"heads": n["dheads"], "dim": n["ddim"]}, "left_scale": 0.7, "right_scale": 0.7}
+    kinds = [("attention", att), ("latent_attention", lat), ("parallel", par), ("attention", att)]
+    layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(s["layers"])]
+    return {"architecture": "Bozovik", "layers": layers, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"], "residual_mult": 0.7,
+            "embedding": {"scale": 1.0}, "token_side": {"dim": n["side"]}, "loop": {"start": 1, "stop": min(3, s["layers"]), "times": 1}}
 
 
 def _time_timerax(serving, folder, prompt_len, batch, ctx, steps, warmup, kernels):
@@ -197,6 +223,28 @@ def run(load_pkg, sizes, prompt_len=4096, batch=64, ctx=512, steps=16, warmup=3,
     for name in sizes:
         s = SIZES[name]
         r = {}
+        if design == "bozovik":
+            bcfg = bozovik_config(s, BOZOVIK[name])
+            tmp = tempfile.mkdtemp(prefix="design_bench_")
+            try:
+                serving.save_model_folder(tmp, bcfg, serving.random_bozovik_tensors(bcfg, 0, decay_rank=64))
+                r["bozovik"] = _time_folder(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)
+                r["bozovik"]["weights_bytes"] = timerax_weight_bytes(bcfg, serving.bozovik_tensor_shapes(bcfg, 64))
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            if not kernels:
+                ncfg = numizen_config(s, NUMIZEN[name], max_positions=max(prompt_len, ctx + steps + warmup) + 64, dense_everywhere=True)
+                tmp = tempfile.mkdtemp(prefix="design_bench_")
+                try:
+                    serving.save_model_folder(tmp, ncfg, serving.random_numizen_tensors(ncfg, 0))
+                    r["numizen_dense"] = _time_folder(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)
+                    r["numizen_dense"]["weights_bytes"] = timerax_weight_bytes(ncfg, serving.numizen_tensor_shapes(ncfg))
+                finally:
+                    shutil.rmtree(tmp, ignore_errors=True)
+                if llama:
+                    r["llama2_bf16_equal_size"] = _time_llama(engine_mod, checkpoint_mod, s, prompt_len, batch, ctx, steps, warmup)
+            results[name] = r
+            continue
         if design == "numizen":
             ncfg = numizen_config(s, NUMIZEN[name], max_positions=max(prompt_len, ctx + steps + warmup) + 64)
             tmp = tempfile.mkdtemp(prefix="design_bench_")

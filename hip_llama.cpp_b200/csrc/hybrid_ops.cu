@@ -1281,29 +1281,41 @@ __global__ void hyb_route_groups_kernel(int experts, int top, int groups, int ke
   if (lane < top) weight[(size_t)r * top + lane] = mine / (sum + 1e-20f);
 }
 
-// any of the feed-forward activations (THA_ACT_*): gated ones read columns col_g and col_u, ungated ones col_u only
+// any of the feed-forward activations (THA_ACT_*): gated ones read a gate value g and an up value u, ungated ones u only.
+// THA_ACT_XIELU arrives with (limit, alpha) = (softplus(p), 1/2 + softplus(q)) of its two stored numbers.
+__device__ __forceinline__ float hyb_act_value(int act, float g, float u, float limit, float alpha) {
+  if (act == THA_ACT_RELU2) {
+    const float p = fmaxf(u, 0.f);
+    return p * p;
+  }
+  if (act == THA_ACT_XIELU) return u > 0.f ? fmaf(limit * u, u, 0.5f * u) : fmaf(alpha, expm1f(u) - u, 0.5f * u);
+  if (act == THA_ACT_GELU_TANH_GLU) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  const float gc = fminf(g, limit);
+  return gc * hyb_sigmoid(alpha * gc) * (fminf(fmaxf(u, -limit), limit) + 1.0f);
+}
 template <typename T>
 __global__ void hyb_ff_act_kernel(T* __restrict__ y, const float* __restrict__ gu, long long ldg, int col_g, int col_u, int n, int ff, int act,
                                   float limit, float alpha) {
-  // THA_ACT_XIELU reads its two stored numbers from (limit, alpha)
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)n * ff) return;
   const size_t r = i / ff; const int c = (int)(i - r * ff);
-  const float u = gu[r * ldg + col_u + c];
-  float v;
-  if (act == THA_ACT_RELU2) {
-    const float p = fmaxf(u, 0.f);
-    v = p * p;
-  } else if (act == THA_ACT_XIELU) {
-    v = u > 0.f ? fmaf(hyb_softplus(limit) * u, u, 0.5f * u) : fmaf(0.5f + hyb_softplus(alpha), expm1f(u) - u, 0.5f * u);
-  } else if (act == THA_ACT_GELU_TANH_GLU) {
-    const float g = gu[r * ldg + col_g + c];
-    v = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
-  } else {
-    const float g = fminf(gu[r * ldg + col_g + c], limit);
-    v = g * hyb_sigmoid(alpha * g) * (fminf(fmaxf(u, -limit), limit) + 1.0f);
-  }
-  hyb_store(y + i, v);
+  const bool gated = act != THA_ACT_RELU2 && act != THA_ACT_XIELU;
+  hyb_store(y + i, hyb_act_value(act, gated ? gu[r * ldg + col_g + c] : 0.f, gu[r * ldg + col_u + c], limit, alpha));
+}
+// the same with four columns per thread and a row per blockIdx.y (sizes and offsets that are multiples of four)
+template <typename T>
+__global__ void hyb_ff_act_vec_kernel(T* __restrict__ y, const float* __restrict__ gu, long long ldg, int col_g, int col_u, int ff, int act,
+                                      float limit, float alpha) {
+  const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (c >= ff) return;
+  const size_t r = blockIdx.y;
+  const bool gated = act != THA_ACT_RELU2 && act != THA_ACT_XIELU;
+  const float4 u = *reinterpret_cast<const float4*>(gu + r * ldg + col_u + c);
+  const float4 g = gated ? *reinterpret_cast<const float4*>(gu + r * ldg + col_g + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float v0 = hyb_act_value(act, g.x, u.x, limit, alpha), v1 = hyb_act_value(act, g.y, u.y, limit, alpha);
+  const float v2 = hyb_act_value(act, g.z, u.z, limit, alpha), v3 = hyb_act_value(act, g.w, u.w, limit, alpha);
+  T* dst = y + r * ff + c;
+  hyb_store(dst, v0); hyb_store(dst + 1, v1); hyb_store(dst + 2, v2); hyb_store(dst + 3, v3);
 }
 
 // counting sort of the (row, pick) pairs by expert, one block, a warp per expert: within an expert the pairs stay in
@@ -1687,11 +1699,26 @@ extern "C" int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* 
 extern "C" int tha_hyb_ff_act(void* stream, int dtype, int act, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
                               int ff, float limit, float alpha) {
   if (n < 1 || ff < 1) return THA_STATUS_SUCCESS;
+  if (act == THA_ACT_XIELU) {   // the two stored numbers p, q -> the factors the kernel multiplies with
+    const float p = limit, q = alpha;
+    limit = fmaxf(p, 0.f) + log1pf(expf(-fabsf(p)));
+    alpha = 0.5f + fmaxf(q, 0.f) + log1pf(expf(-fabsf(q)));
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool gated = act != THA_ACT_RELU2 && act != THA_ACT_XIELU;
+  if (ff % 4 == 0 && ldg % 4 == 0 && col_u % 4 == 0 && (!gated || col_g % 4 == 0) && aligned16(gu) && n <= 65535) {
+    const dim3 grid(ceil_div(ff / 4, 128), n);
+    if (dtype == THA_DT_BF16)
+      THA_CUDA_OK(launch(hyb_ff_act_vec_kernel<bf16>, grid, dim3(128), 0, s, false, (bf16*)y, gu, ldg, col_g, col_u, ff, act, limit, alpha));
+    else
+      THA_CUDA_OK(launch(hyb_ff_act_vec_kernel<float>, grid, dim3(128), 0, s, false, (float*)y, gu, ldg, col_g, col_u, ff, act, limit, alpha));
+    return THA_STATUS_SUCCESS;
+  }
   const dim3 grid((unsigned)(((size_t)n * ff + 255) / 256));
   if (dtype == THA_DT_BF16)
-    THA_CUDA_OK(launch(hyb_ff_act_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, false, (bf16*)y, gu, ldg, col_g, col_u, n, ff, act, limit, alpha));
+    THA_CUDA_OK(launch(hyb_ff_act_kernel<bf16>, grid, dim3(256), 0, s, false, (bf16*)y, gu, ldg, col_g, col_u, n, ff, act, limit, alpha));
   else
-    THA_CUDA_OK(launch(hyb_ff_act_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, false, (float*)y, gu, ldg, col_g, col_u, n, ff, act, limit, alpha));
+    THA_CUDA_OK(launch(hyb_ff_act_kernel<float>, grid, dim3(256), 0, s, false, (float*)y, gu, ldg, col_g, col_u, n, ff, act, limit, alpha));
   return THA_STATUS_SUCCESS;
 }
 

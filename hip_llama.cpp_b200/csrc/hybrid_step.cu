@@ -95,10 +95,11 @@ struct Carver {
 
 struct StepBuffers {
   float *x, *proj, *q, *left, *right, *conv, *dt_raw, *gate_raw, *gu, *down, *sdown, *weight, *oraw, *split; size_t split_floats;
-  float *proj2, *qfull, *x0;
+  float *proj2, *qfull, *x0, *sgate;
+  void* sg;
   void *h, *h2, *cq, *qplain, *abuf, *mbuf, *y, *sy, *hn, *hg;
   int *expert_id, *group_off, *sorted_row, *inv;
-  float* cos_t[16]; float* sin_t[16];
+  float* cos_t[64]; float* sin_t[64];
 };
 
 // Steps of at least this many rows MAY run a mixture's experts as one tensor-core matmul per expert (the group sizes
@@ -117,10 +118,12 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
   size_t n_in = 0, qd = 0, av = 0, mv = 0, cc = 0, dd = 0, dg = 0, gu = 0, ff = 0, sff = 0, top = 0, ne = 0;
   size_t n_in2 = 0, qr = 0, qf = 0, qp = 0;
   bool norm2 = false, keep_embed = false;
+  size_t sd = 0;
   for (int i = 0; i < m->n_layers; i++) {
     const tha_hyb_layer_t& L = m->layers[i];
     n_in = max(n_in, (size_t)L.n_in);
     if (L.pre_add_embed) keep_embed = true;
+    sd = max(sd, (size_t)L.side.dim);
     if (L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) {
       qd = max(qd, (size_t)L.attn.heads * L.attn.dim);
       av = max(av, (size_t)L.attn.heads * L.attn.vdim);
@@ -194,8 +197,10 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
   b->sorted_row = c.take<int>(R * top);
   b->inv = c.take<int>(R * top);
   b->group_off = c.take<int>(2 * (ne + 1));
+  b->sgate = c.take<float>(R * sd);
+  b->sg = c.take<char>(R * sd * es);
   b->hn = c.take<char>((size_t)n_want * W * es);
-  for (int i = 0; i < m->n_rot && i < 16; i++) {
+  for (int i = 0; i < m->n_rot && i < 64; i++) {
     b->cos_t[i] = c.take<float>((size_t)R * (m->rot[i].dims / 2));
     b->sin_t[i] = c.take<float>((size_t)R * (m->rot[i].dims / 2));
   }
@@ -215,7 +220,7 @@ typedef __nv_bfloat16 bf16;
 
 extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_rows_t* rows, const tha_kv_t* kv,
                             const tha_state_store_t* st, int n_want, const int* want_rows, float* logits, float* taps) {
-  if (!m || !rows || !kv || !st || m->n_rot > 16) return THA_STATUS_INVALID_ARG;
+  if (!m || !rows || !kv || !st || m->n_rot > 64) return THA_STATUS_INVALID_ARG;
   const int R = rows->n_rows;
   if (R < 1) return THA_STATUS_SUCCESS;
   cudaStream_t s = (cudaStream_t)stream;
@@ -245,12 +250,14 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
                        (const float*)m->pos_embed, rows->pos, embed_scale, b.x0));
   for (int i = 0; i < m->n_rot; i++) HYB_OK(tha_hyb_rotary_table(stream, &m->rot[i], rows->pos, R, b.cos_t[i], b.sin_t[i]));
 
+  bool h_ready = false;   // the previous block's last pass already left this layer's first norm in b.h
   for (int li = 0; li < m->n_layers; li++) {
     const tha_hyb_layer_t& L = m->layers[li];
     const long long ldp = L.n_in;
     const bool seq = L.block == THA_BLOCK_SEQUENTIAL;
     const bool two_norms = !seq && L.has_norm2 && L.has_ff != THA_FF_NONE;
-    if (seq && (L.pre_add_embed || L.pre_vec))   // a pass's re-entry addends and the mixer's norm in one pass over x
+    if (seq && h_ready) h_ready = false;
+    else if (seq && (L.pre_add_embed || L.pre_vec))   // a pass's re-entry addends and the mixer's norm in one pass over x
       HYB_OK(tha_hyb_add_norm(stream, dt, b.x, nullptr, 0.f, nullptr, 0.f, L.pre_add_embed ? b.x0 : nullptr, L.pre_vec, &L.norm1, m->eps, b.h, R, W));
     else if (two_norms) HYB_OK(tha_hyb_norm_pair(stream, dt, b.h, b.h2, b.x, &L.norm1, &L.norm2, m->eps, R, W));
     else HYB_OK(tha_hyb_norm(stream, dt, b.h, b.x, &L.norm1, m->eps, R, W, nullptr));
@@ -344,8 +351,24 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       } else {
         return THA_STATUS_NOT_SUPPORTED;
       }
-      HYB_OK(tha_hyb_side_finish(stream, dt, b.x, ffo, m_res, &L.side, m->side_table, m->side_cols, rows->token, m->eps, R, W,
-                                 taps ? taps + (size_t)li * R * W : (float*)nullptr));
+      const float* y = nullptr;
+      if (L.side.dim > 0) {
+        // the side input reads the stream after the feed-forward: x += m * ff and x in the products' number format, the gate
+        // product, its activation times the token's table entries, the projection
+        const tha_norm_t copy = {THA_NORM_COPY};
+        HYB_OK(tha_hyb_add_norm(stream, dt, b.x, ffo, m_res, nullptr, 0.f, nullptr, nullptr, &copy, m->eps, b.h, R, W));
+        ffo = nullptr;
+        HYB_OK(tha_hyb_linear(stream, dt, b.sgate, L.side.dim, b.h, W, 0, nullptr, L.side.w_gate, 0, R, L.side.dim, W, nullptr, 0));
+        HYB_OK(tha_hyb_side_gate(stream, dt, b.sg, b.sgate, L.side.dim, &L.side, m->side_table, m->side_cols, rows->token, R));
+        HYB_OK(tha_hyb_linear(stream, dt, b.sdown, W, b.sg, L.side.dim, 0, nullptr, L.side.w_proj, 0, R, W, L.side.dim, nullptr, 0));
+        y = b.sdown;
+      }
+      // the last pass over x: the remaining residual adds, the tap, and what comes ahead of the next layer run
+      const tha_hyb_layer_t* next = li + 1 < m->n_layers && m->layers[li + 1].block == THA_BLOCK_SEQUENTIAL ? &m->layers[li + 1] : nullptr;
+      HYB_OK(tha_hyb_block_finish(stream, dt, b.x, ffo, y, m_res, L.side.norm, m->eps, taps ? taps + (size_t)li * R * W : (float*)nullptr,
+                                  next && next->pre_add_embed ? b.x0 : nullptr, next ? next->pre_vec : nullptr, next ? &next->norm1 : nullptr,
+                                  next ? b.h : nullptr, R, W));
+      h_ready = next != nullptr;
       continue;
     }
     // the feed-forward reads the mixer's normed input, or a second norm of the same x through its own stacked product

@@ -136,6 +136,9 @@ void SafeTensors::read_f32(const std::string& name, std::vector<float>* out) con
   } else if (t.dtype == "F32") {
     if (t.end - t.begin != 4 * n) throw std::runtime_error("tensor '" + name + "': size does not fit its shape");
     for (size_t i = 0; i < n; i++) { float f; memcpy(&f, p + 4 * i, 4); out->push_back(f); }
+  } else if (t.dtype == "I32") {   // integer tables, read as numbers
+    if (t.end - t.begin != 4 * n) throw std::runtime_error("tensor '" + name + "': size does not fit its shape");
+    for (size_t i = 0; i < n; i++) { int32_t v; memcpy(&v, p + 4 * i, 4); out->push_back((float)v); }
   } else {
     throw std::runtime_error("tensor '" + name + "': dtype " + t.dtype + " is not served");
   }
@@ -593,7 +596,7 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       }
     }
     m->state_floats_ = state > 0 ? state : 1;
-    if (m->rot_.size() > 16) throw std::runtime_error("more than 16 distinct rotary tables");
+    if (m->rot_.size() > 64) throw std::runtime_error("more than 64 distinct rotary tables");
     tha_hyb_model_t& M = m->model_;
     M.dtype = dtype;
     M.width = W;

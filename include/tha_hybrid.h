@@ -43,6 +43,7 @@ extern "C" {
 #define THA_NORM_RMS 0     /* x / sqrt(mean(x^2) + eps) * (w_offset + w) */
 #define THA_NORM_DYT 1     /* tanh(alpha * x) * w + b: element-wise, no statistics */
 #define THA_NORM_LAYER 2   /* (x - mean) / sqrt(variance + eps) * w + b, variance = mean of the squared deviations */
+#define THA_NORM_COPY 3    /* x itself in the product's number format (tha_hyb_add_norm, tha_hyb_block_finish) */
 
 #define THA_FF_NONE 0
 #define THA_FF_MOE 1
@@ -362,12 +363,17 @@ int tha_hyb_gdelta_scan(void* stream, int dtype, const tha_gdelta_t* g, const th
                         float* proj, long long ldp, float* w_raw, float* o_raw, void* out);
 /* floats of one sequence's state of a generalized-delta-rule layer */
 long long tha_hyb_gdelta_state_floats(int heads, int dim);
-/* the end of a sequential block: x += m * ff (ff NULL: none), then the side input of tha_side_t (side->dim 0: none);
- * tap (nullable) receives x */
-int tha_hyb_side_finish(void* stream, int dtype, float* x, const float* ff, float m, const tha_side_t* side, const void* side_table,
-                        int side_cols, const int* token, float eps, int n_rows, int width, float* tap);
+/* out (dtype-typed [n_rows, side->dim]) = gelu_tanh(gate_raw) * table[token, side->col0 ..]: the input of the side projection */
+int tha_hyb_side_gate(void* stream, int dtype, void* out, const float* gate_raw, long long ldg, const tha_side_t* side,
+                      const void* side_table, int side_cols, const int* token, int n_rows);
+/* the end of a sequential block, one pass over x: x += m * ff (ff NULL: none); x += m * y / sqrt(mean(y^2) + eps) * y_norm
+ * (y NULL: none); tap (nullable) receives x; then x += embed_out (nullable), x += vec (nullable), and with next_norm not
+ * NULL out (dtype-typed) = that norm of x -- what comes ahead of the next layer run */
+int tha_hyb_block_finish(void* stream, int dtype, float* x, const float* ff, const float* y, float m, const float* y_norm, float eps,
+                         float* tap, const float* embed_out, const float* vec, const tha_norm_t* next_norm, void* out, int n_rows,
+                         int width);
 /* x += c_left * left + c_right * right (right NULL: none) (+ embed_out when given) (+ vec when given); then, with n not NULL,
- * out (dtype-typed) = the norm n of x.  left NULL: only the optional addends. */
+ * out (dtype-typed) = the norm n of x (THA_NORM_COPY: x itself).  left NULL: only the optional addends. */
 int tha_hyb_add_norm(void* stream, int dtype, float* x, const float* left, float c_left, const float* right, float c_right,
                      const float* embed_out, const float* vec, const tha_norm_t* n, float eps, void* out, int n_rows, int width);
 /* softmax attention of every row over its visible cache rows; out dtype-typed [n_rows, heads * vdim].
