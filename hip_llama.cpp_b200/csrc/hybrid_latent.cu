@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(128 * MT) hyb_attn_wide_kernel(tha_attn_t a, t
   float* m_s = corr_s + PAIRS;                                             // [PAIRS] running maxima at the end
   int seq = -1, r0 = 0, r_end = 0;
   {
-    int tile = blockIdx.x / splits;
+    // the last tiles of a prompt see the most keys: they start first, so that the grid does not end on its longest blocks
+    int tile = (int)(gridDim.x / splits) - 1 - (int)(blockIdx.x / splits);
     for (int s = 0; s < rows.n_seqs; s++) {
       const int lo = rows.seq_first[s], hi = rows.seq_first[s + 1];
       const int nt = (hi - lo + AP - 1) / AP;

@@ -326,7 +326,8 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
   // which sequence and which positions: tiles of AP rows per sequence, found by walking the sequences
   int seq = -1, r0 = 0, r_end = 0;
   {
-    int tile = blockIdx.x / splits;
+    // the last tiles of a prompt see the most keys: they start first, so that the grid does not end on its longest blocks
+    int tile = (int)(gridDim.x / splits) - 1 - (int)(blockIdx.x / splits);
     for (int s = 0; s < rows.n_seqs; s++) {
       const int lo = rows.seq_first[s], hi = rows.seq_first[s + 1];
       const int nt = (hi - lo + AP - 1) / AP;
@@ -533,7 +534,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <bool EXACT>
-__global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
+__global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t kv, const float* __restrict__ q,
                                                            __nv_bfloat16* __restrict__ out, int AG, int AP, int splits,
                                                            float* __restrict__ partial, const float* __restrict__ gate, long long ldg) {
   extern __shared__ __align__(16) unsigned char smraw[];
@@ -543,7 +544,8 @@ __global__ void __launch_bounds__(128) hyb_attn_mma_kernel(tha_attn_t a, tha_row
   __nv_bfloat16* Vt = Ks + ATT_KEYS * KS;                        // [E][VS]
   int seq = -1, r0 = 0, r_end = 0;
   {
-    int tile = blockIdx.x / splits;
+    // the last tiles of a prompt see the most keys: they start first, so that the grid does not end on its longest blocks
+    int tile = (int)(gridDim.x / splits) - 1 - (int)(blockIdx.x / splits);
     for (int s = 0; s < rows.n_seqs; s++) {
       const int lo = rows.seq_first[s], hi = rows.seq_first[s + 1];
       const int nt = (hi - lo + AP - 1) / AP;
