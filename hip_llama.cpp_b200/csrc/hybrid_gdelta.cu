@@ -1,6 +1,6 @@
 // Generalized delta rule (tha_gdelta_t): per head, with a decay w and a removal rate a per key channel and the unit key
 // u = k / sqrt(sum(k^2) + 1e-6),
-//     S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T      (S on the right: the state before the token, throughout),   o_t = S_t^T r_t.
+//     S' = diag(w) S - (a o u)(u^T S) + k v^T   (S on the right is the state before the token throughout),   o = S'^T r.
 //   hyb_tanh_cols_kernel     the low-rank decay input in place: columns of the stacked projection -> their tanh
 //   hyb_gdelta_gates_kernel  all rows at once, in place: z_w + w0 -> w = exp(-exp(-1/2) * sigmoid(z_w + w0)) and the removal
 //                            columns of the projection z_a + a_b -> a = sigmoid(z_a + a_b)

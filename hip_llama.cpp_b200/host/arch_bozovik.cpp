@@ -14,8 +14,8 @@
 //                       summed with two constants.
 // Feed-forward: none, or dense without a gate, W_down xielu(W_up h).
 // "loop" runs a segment of the layer list several times with the same weights, every pass with a cache and state of its
-// own; from the second pass on a pass starts by adding the embedding output to x again; every pass adds the learned vector of the
-// pass.  Every size and constant comes from the config; constants the design fixes live with the mechanisms.
+// own; from the second pass on a pass starts by adding the embedding output to x again, and every pass then adds its own
+// learned vector.  Every size and constant comes from the config; constants the design fixes live with the mechanisms.
 #include <math.h>
 
 #include "layer_model.hpp"

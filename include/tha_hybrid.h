@@ -112,7 +112,8 @@ typedef struct {
 /* Softmax attention over the cache.  A query at position p sees the keys j <= p with
  * floor(j / chunk) == floor(p / chunk) when chunk > 0, every j <= p otherwise; with window > 0 only those of them with
  * p - j < window or j < keep_first (nothing is renumbered: rotation and distances use absolute positions).
- * sink (per head): one more term exp(sink[h]) in the softmax's normalising sum; it brings no value and is not scaled.
+ * sink (per head): one more term exp(sink[h]) in the softmax's normalising sum; it brings no value, and neither `scale` nor
+ * head_scale applies to it.
  * head_scale (per head): the scores of head h are multiplied by head_scale[h] on top of `scale`.
  * Output gate per head: head h's result is multiplied by sigmoid of column o_g + h of the stacked projection. */
 typedef struct {
@@ -141,7 +142,7 @@ typedef struct {
 /* Generalized delta rule with a decay and a removal rate per key channel.  r, k, v, g: heads x dim columns each.
  *   decay   w = exp(-exp(-1/2) * sigmoid(W_w2 tanh(W_w1 h) + w0))      removal rate   a = sigmoid(W_a h + a_b)
  *   unit key u = k / sqrt(sum(k^2) + 1e-6) per head
- *   S_t = diag(w) S_(t-1) - (a * u) (u^T S_(t-1)) + k v^T  (S on the right: the state before the token, throughout),   o_t = S_t^T r
+ *   S' = diag(w) S - (a o u)(u^T S) + k v^T  (S on the right: the state before the token, throughout),   o = S'^T r
  * The read-out is divided by its root mean square per head, weighted (norm, [heads * dim]) and gated by sigmoid(g).
  * State per head: dim x dim floats laid out for the scan ([column pair][key channel][2], an odd last column padded). */
 typedef struct {

@@ -96,7 +96,7 @@ def sink_softmax(s, vis, sink):
 
 # ---- softmax attention (grouped heads; used alone and as the left side of a parallel mixer) -----------------------
 def attention_mixer(h, m, W, p, cache, pos0, kind):
-    """kind 'attention': causal, per-head temperature, a constant 1 in the normalising sum;
+    """kind 'attention': causal, a factor per head on the scores, a sink fixed at zero (a constant 1 in the normalising sum);
     kind 'left': window with kept first tokens, learned sink.  cache: dict with 'k', 'v' of the earlier positions."""
     T = len(h)
     H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
