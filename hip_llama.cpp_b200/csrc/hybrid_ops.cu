@@ -750,10 +750,12 @@ __global__ void hyb_attn_merge_kernel(T* __restrict__ out, const float* __restri
   if (lane < splits) { const float ms = p0[lane * stride + E]; w = ms > -INFINITY ? expf(ms - M) : 0.f; }
   const int row = idx / heads, head = idx - row * heads;
   const float fin = hyb_attn_final_factor(a, head, M, L, gate ? gate + (size_t)row * ldg : nullptr);
-  for (int e = lane; e < E; e += 32) {
+  // every lane walks every group of 32 channels (the shuffles need the whole warp), also where E is not a multiple of 32
+  for (int e0 = 0; e0 < E; e0 += 32) {
+    const int e = e0 + lane;
     float o = 0.f;
-    for (int s = 0; s < splits; s++) { const float ws = __shfl_sync(THA_FULL_MASK, w, s); if (ws > 0.f) o = fmaf(p0[s * stride + e], ws, o); }
-    hyb_store(out + (size_t)idx * E + e, o * fin);
+    for (int s = 0; s < splits; s++) { const float ws = __shfl_sync(THA_FULL_MASK, w, s); if (ws > 0.f && e < E) o = fmaf(p0[s * stride + e], ws, o); }
+    if (e < E) hyb_store(out + (size_t)idx * E + e, o * fin);
   }
 }
 

@@ -453,6 +453,20 @@ def test_a_sink_takes_its_share(tmp_path):
         assert rel_err(feed(b.engine(), "a", toks, [20, 1]), z) < F32_TOL
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", F32_TOL), ("bfloat16", BF16_TOL)])
+def test_few_rows_at_a_long_context_with_value_rows_that_are_no_multiple_of_a_warp(tmp_path, dtype, tol):
+    """Steps of one or two rows behind hundreds of positions are cut along the keys into up to sixteen parts and merged; with
+    40 or 72 value channels the last group of channels is ragged, and every part's factor must still reach it."""
+    cfg = model([attention(dense(), heads=6, kv_heads=2, dim=32, vdim=40, rot_dims=16),
+                 parallel(None, left=attn(heads=4, kv_heads=2, dim=16, vdim=72, mask=(900, 2)), heads=1, dim=20)], width=64, vocab=120)
+    b = Built(tmp_path, cfg, 7)
+    toks = tokens_for(b, 720, 4)
+    z, _ = b.ref(toks)
+    got = feed(b.engine(dtype), "a", toks, [600, 38, 2, 1, 1, 2, 3, 1])
+    assert max(rel_err(g, w) for g, w in zip(got[600:], z[600:])) < 3 * tol
+    assert rel_err(got, z) < tol
+
+
 # ---- the tensor-core attention forms of the bfloat16 number format ------------------------------------------------------
 @pytest.mark.parametrize("kind", ["attention", "left", "latent", "wide_latent"])
 @pytest.mark.parametrize("cuts", [[300], [150, 86, 2, 1], [64, 1]])
