@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
 // ------------------------------------------------------------------------------------------------------------------
 // the same attention on the tensor cores, for the bf16 number format and heads of up to 128 channels (multiples of 16 /
 // 8): a block takes 64 (position, query head) pairs of one K/V head, each of its 4 warps 16 of them.  Per tile of 32 keys
-// (aligned to absolute multiples of 32 as above): K rows and TRANSPOSED V rows go to shared memory as bf16; a warp
+// (aligned to absolute multiples of 32 as above): K rows and V rows go to shared memory as bf16, both row-major; a warp
 // computes its 16 x 32 scores with mma.sync m16n8k16 (q as the A operand from registers), scales and masks them in fp32,
 // keeps the online softmax of its rows among the four lanes that share a row, rounds the weights to bf16 (the row sums
 // add the rounded weights, so that they still sum to one) and multiplies them with V straight from the score registers:
@@ -539,9 +539,10 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
                                                            float* __restrict__ partial, const float* __restrict__ gate, long long ldg) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int D = a.dim, E = a.vdim, gsize = a.heads / a.kv_heads;
-  const int KS = D + 8, VS = ATT_KEYS + 8;               // padded rows: conflict-free fragment reads
+  const int KS = D + 8, VS = E + 8;                      // padded rows: conflict-free fragment and ldmatrix reads
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);   // [32][KS]
-  __nv_bfloat16* Vt = Ks + ATT_KEYS * KS;                        // [E][VS]
+  __nv_bfloat16* Vs = Ks + ATT_KEYS * KS;                        // [32][VS], row-major like the cache: transposed on the way out
+  const unsigned vs_base = (unsigned)__cvta_generic_to_shared(Vs);
   int seq = -1, r0 = 0, r_end = 0;
   {
     // the last tiles of a prompt see the most keys: they start first, so that the grid does not end on its longest blocks
@@ -600,6 +601,8 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
     ti_begin = sp * per;
     ti_end = min(tiles.n, ti_begin + per);
   }
+  // cache rows start on 16-byte boundaries when the pool's row pitch and the heads' offsets are multiples of four floats
+  const bool vec4 = (kv.kv_dim & 3) == 0 && ((D | E) & 3) == 0 && ((reinterpret_cast<size_t>(kv.k_pool) | reinterpret_cast<size_t>(kv.v_pool)) & 15) == 0;
   for (int ti = ti_begin; ti < ti_end; ti++) {
     const int kt = ti < tiles.n_a ? tiles.begin + ATT_KEYS * ti : tiles.resume + ATT_KEYS * (ti - tiles.n_a);
     __syncthreads();
@@ -610,6 +613,32 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
       const int t = kt + warp + 4 * jj;
       krow[jj] = (t <= p_last && t >= key_lo) ? hyb_kv_row(kv, slot, t, a.cache_layer) : (size_t)-1;
     }
+    if (vec4) {
+      // 16-byte aligned cache rows: a lane takes four channels of a row in one 128-bit load (eight rows in flight) and leaves
+      // them as four bf16 in one 64-bit store
+#pragma unroll
+      for (int which = 0; which < 2; which++) {
+        const float* pool = which ? kv.v_pool : kv.k_pool;
+        const int width4 = (which ? E : D) >> 2;
+        float4 buf[ATT_KEYS / 4];
+#pragma unroll
+        for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
+          const bool live = krow[jj] != (size_t)-1 && lane < width4;
+          const float4* src = reinterpret_cast<const float4*>(pool + (live ? krow[jj] : 0) + (size_t)g * (width4 << 2));
+          buf[jj] = live ? __ldg(src + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (lane < width4) {
+#pragma unroll
+          for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
+            const int j = warp + 4 * jj;
+            uint2 pk;
+            pk.x = pack_bf16(buf[jj].x, buf[jj].y);
+            pk.y = pack_bf16(buf[jj].z, buf[jj].w);
+            *reinterpret_cast<uint2*>((which ? Vs + j * VS : Ks + j * KS) + 4 * lane) = pk;
+          }
+        }
+      }
+    } else {
 #pragma unroll
     for (int which = 0; which < 2; which++) {
       const float* pool = which ? kv.v_pool : kv.k_pool;
@@ -631,12 +660,13 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
           for (int c = 0; c < AM_MAXD / 32; c++) {
             const int d = lane + 32 * c;
             if (d < width) {
-              if (which) Vt[d * VS + j] = __float2bfloat16_rn(buf[jj][c]);
+              if (which) Vs[j * VS + d] = __float2bfloat16_rn(buf[jj][c]);
               else Ks[j * KS + d] = __float2bfloat16_rn(buf[jj][c]);
             }
           }
         }
       }
+    }
     }
     __syncthreads();
     // scores of this warp's 16 pairs against the 32 keys
@@ -698,18 +728,27 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
 #pragma unroll
       for (int n = 0; n < AM_MAXD / 8; n++) { oacc[n][2 * x] *= corr; oacc[n][2 * x + 1] *= corr; }
     }
-    // weights times values: two k steps of 16 keys
+    // weights times values: two k steps of 16 keys, two channel tiles per ldmatrix.  Values [key][channel] row-major,
+    // transposed on the way: lanes 0..15 name the rows of keys 16 t2 + (lane & 15) at this channel tile, lanes 16..31 the same
+    // keys at the next one (an odd last tile reads its own twice)
 #pragma unroll
-    for (int n = 0; n < AM_MAXD / 8; n++) {
+    for (int n = 0; n < AM_MAXD / 8; n += 2) {
       if (8 * n < E) {
+        const bool two = 8 * (n + 1) < E;
 #pragma unroll
         for (int t2 = 0; t2 < 2; t2++) {
-          uint32_t b[2];
-          const __nv_bfloat16* vr = Vt + (8 * n + lr) * VS + 16 * t2 + lc;
-          b[0] = *reinterpret_cast<const uint32_t*>(vr);
-          b[1] = *reinterpret_cast<const uint32_t*>(vr + 8);
-          mma_bf16_16816(oacc[n], pa[t2], b);
-          if (EXACT) mma_bf16_16816(oacc[n], pl[t2], b);
+          uint32_t vf[4];
+          const int ch = 8 * n + ((two && lane >= 16) ? 8 : 0);
+          const unsigned addr = vs_base + (unsigned)(((16 * t2 + (lane & 15)) * VS + ch) * sizeof(__nv_bfloat16));
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(vf[0]), "=r"(vf[1]), "=r"(vf[2]), "=r"(vf[3]) : "r"(addr));
+          const uint32_t v0[2] = {vf[0], vf[1]}, v1[2] = {vf[2], vf[3]};
+          mma_bf16_16816(oacc[n], pa[t2], v0);
+          if (EXACT) mma_bf16_16816(oacc[n], pl[t2], v0);
+          if (two) {
+            mma_bf16_16816(oacc[n + 1], pa[t2], v1);
+            if (EXACT) mma_bf16_16816(oacc[n + 1], pl[t2], v1);
+          }
         }
       }
     }
@@ -1539,7 +1578,7 @@ extern "C" int tha_hyb_attn_gated(void* stream, int dtype, const tha_attn_t* a, 
   const bool wide = !tc && !gate && !a->head_scale && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && hyb_attn_wide_ok(a);
   const int pairs = wide ? hyb_attn_wide_pairs(a, rows) : tc ? AM_PAIRS : ATT_PAIRS;
   const int AG = gsize < pairs ? gsize : pairs, AP = pairs / AG;
-  const size_t smem = tc ? sizeof(__nv_bfloat16) * ((size_t)ATT_KEYS * (a->dim + 8) + (size_t)a->vdim * (ATT_KEYS + 8))
+  const size_t smem = tc ? sizeof(__nv_bfloat16) * ((size_t)ATT_KEYS * (a->dim + 8) + (size_t)ATT_KEYS * (a->vdim + 8))
                          : sizeof(float) * ((size_t)ATT_PAIRS * a->dim + (size_t)ATT_KEYS * (a->dim + 4) + (size_t)ATT_KEYS * a->vdim + ATT_PAIRS * ATT_KEYS);
   if (!wide && smem > 227 * 1024) return THA_STATUS_NOT_SUPPORTED;
   // position tiles: at most one ragged tile per sequence beyond rows / AP
