@@ -281,9 +281,13 @@ __global__ void hyb_attn_prepare_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t 
   const float* pr = proj + (size_t)r * ldp;
   const int half = rot_dims / 2;
   const size_t krow = hyb_kv_row(kv, slot, t, a.cache_layer);
-  for (int h = warp; h < a.heads + 2 * a.kv_heads; h += nwarps) {
-    if (h >= a.heads + a.kv_heads) {   // a value head: plain copy
-      const int g = h - a.heads - a.kv_heads;
+  // a layer that reads another layer's cache rows prepares its queries only; key heads that share a value head write it once
+  const int n_k = a.kv_shared ? 0 : a.kv_heads, n_v = a.kv_shared ? 0 : a.kv_heads / (a.v_share > 1 ? a.v_share : 1);
+  // queries grow with the logarithm of their position, in steps of q_temp_every positions
+  const float q_mult = a.q_temp_every > 0 ? 1.0f + a.q_temp_coef * logf((float)((t + 1) / a.q_temp_every + 1)) : 1.0f;
+  for (int h = warp; h < a.heads + n_k + n_v; h += nwarps) {
+    if (h >= a.heads + n_k) {   // a value head: plain copy
+      const int g = h - a.heads - n_k;
       for (int e = lane; e < a.vdim; e += 32) kv.v_pool[krow + (size_t)g * a.vdim + e] = pr[a.o_v + g * a.vdim + e];
       continue;
     }
@@ -294,9 +298,11 @@ __global__ void hyb_attn_prepare_kernel(tha_attn_t a, tha_rows_t rows, tha_kv_t 
     const float* cr = cos_t + (size_t)r * half;
     const float* sr = sin_t + (size_t)r * half;
     float ss = 0.f;
-    for (int d = lane; d < a.dim; d += 32) { const float v = hyb_rotated(src, d, rot_dims, a.rot_layout, cr, sr); ss = fmaf(v, v, ss); }
-    ss = warp_sum(ss);
-    const float inv = a.unit_rms ? 1.0f / sqrtf(ss / (float)a.dim + a.eps) : 1.0f;
+    if (a.unit_rms) {
+      for (int d = lane; d < a.dim; d += 32) { const float v = hyb_rotated(src, d, rot_dims, a.rot_layout, cr, sr); ss = fmaf(v, v, ss); }
+      ss = warp_sum(ss);
+    }
+    const float inv = (a.unit_rms ? 1.0f / sqrtf(ss / (float)a.dim + a.eps) : 1.0f) * (is_q ? q_mult : 1.0f);
     for (int d = lane; d < a.dim; d += 32) dst[d] = hyb_rotated(src, d, rot_dims, a.rot_layout, cr, sr) * inv;
   }
 }
@@ -337,6 +343,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     if (seq < 0) return;
   }
   const int g = blockIdx.y, part = blockIdx.z;
+  const int gv = a.v_share > 1 ? g / a.v_share : g;   // the value head this key head reads
   const int slot = rows.seq_slot[seq];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int p_first = rows.pos[r0], p_last = p_first + (r_end - r0) - 1;
@@ -386,6 +393,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
     for (int which = 0; which < 2; which++) {
       const float* pool = which ? kv.v_pool : kv.k_pool;
       const int width = which ? E : D, stride = which ? E : KS;
+      const int gh = which ? gv : g;
       float* dst = which ? Vs : Ks;
 #pragma unroll
       for (int j0 = 0; j0 < ATT_KEYS / 4; j0 += 4) {
@@ -393,7 +401,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
 #pragma unroll
         for (int jj = 0; jj < 4; jj++) {
           const bool live = krow[j0 + jj] != (size_t)-1;
-          const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
+          const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)gh * width;
 #pragma unroll
           for (int c = 0; c < VC; c++) buf[jj][c] = (live && lane + 32 * c < width) ? __ldg(src + lane + 32 * c) : 0.f;
         }
@@ -405,7 +413,7 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
             if (lane + 32 * c < width) dst[j * stride + lane + 32 * c] = buf[jj][c];
           if (width > 32 * VC) {   // wider key rows than the register buffer: the rest one by one
             const bool live = krow[j0 + jj] != (size_t)-1;
-            const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
+            const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)gh * width;
             for (int d = lane + 32 * VC; d < width; d += 32) dst[j * stride + d] = live ? src[d] : 0.f;
           }
         }
@@ -512,7 +520,11 @@ __global__ void __launch_bounds__(128) hyb_attn_kernel(tha_attn_t a, tha_rows_t 
 #pragma unroll
     for (int c = 0; c < VC; c++) {
       const int e = lane + 32 * c;
-      if (e < E) hyb_store(out + (size_t)r * a.heads * E + (size_t)h * E + e, acc[rr][c] * inv);
+      if (e < E) {
+        const size_t at = (size_t)r * a.heads * E + (size_t)h * E + e;
+        if (a.out_f32) reinterpret_cast<float*>(out)[at] = acc[rr][c] * inv;
+        else hyb_store(out + at, acc[rr][c] * inv);
+      }
     }
   }
 }
@@ -556,6 +568,7 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
     if (seq < 0) return;
   }
   const int g = blockIdx.y, part = blockIdx.z;
+  const int gv = a.v_share > 1 ? g / a.v_share : g;   // the value head this key head reads
   const int slot = rows.seq_slot[seq];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int p_first = rows.pos[r0], p_last = p_first + (r_end - r0) - 1;
@@ -624,7 +637,7 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
 #pragma unroll
         for (int jj = 0; jj < ATT_KEYS / 4; jj++) {
           const bool live = krow[jj] != (size_t)-1 && lane < width4;
-          const float4* src = reinterpret_cast<const float4*>(pool + (live ? krow[jj] : 0) + (size_t)g * (width4 << 2));
+          const float4* src = reinterpret_cast<const float4*>(pool + (live ? krow[jj] : 0) + (size_t)(which ? gv : g) * (width4 << 2));
           buf[jj] = live ? __ldg(src + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         if (lane < width4) {
@@ -643,13 +656,14 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
     for (int which = 0; which < 2; which++) {
       const float* pool = which ? kv.v_pool : kv.k_pool;
       const int width = which ? E : D;
+      const int gh = which ? gv : g;
 #pragma unroll
       for (int j0 = 0; j0 < ATT_KEYS / 4; j0 += 4) {
         float buf[4][AM_MAXD / 32];
 #pragma unroll
         for (int jj = 0; jj < 4; jj++) {
           const bool live = krow[j0 + jj] != (size_t)-1;
-          const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)g * width;
+          const float* src = pool + (live ? krow[j0 + jj] : 0) + (size_t)gh * width;
 #pragma unroll
           for (int c = 0; c < AM_MAXD / 32; c++) buf[jj][c] = (live && lane + 32 * c < width) ? __ldg(src + lane + 32 * c) : 0.f;
         }
@@ -765,6 +779,13 @@ __global__ void __launch_bounds__(128, 3) hyb_attn_mma_kernel(tha_attn_t a, tha_
       continue;
     }
     const float inv = hyb_attn_final_factor(a, row_h[x], m_run[x], l_run[x], gate ? gate + (size_t)row_r[x] * ldg : nullptr);
+    if (a.out_f32) {
+      float* dst = reinterpret_cast<float*>(out) + (size_t)row_r[x] * a.heads * E + (size_t)row_h[x] * E;
+#pragma unroll
+      for (int n = 0; n < AM_MAXD / 8; n++)
+        if (8 * n < E) *reinterpret_cast<float2*>(dst + 8 * n + lc) = make_float2(oacc[n][2 * x] * inv, oacc[n][2 * x + 1] * inv);
+      continue;
+    }
     __nv_bfloat16* dst = out + (size_t)row_r[x] * a.heads * E + (size_t)row_h[x] * E;
 #pragma unroll
     for (int n = 0; n < AM_MAXD / 8; n++)
@@ -1122,20 +1143,25 @@ __global__ void hyb_head_gate_kernel(T* __restrict__ out, const float* __restric
 // ------------------------------------------------------------------------------------------------------------------
 // short causal convolution + silu; the slot keeps the last taps-1 inputs of every channel (oldest first)
 // ------------------------------------------------------------------------------------------------------------------
-__global__ void hyb_conv_silu_kernel(tha_rows_t rows, tha_state_store_t st, long long conv_state_off, const float* __restrict__ proj,
-                                     long long ldp, int col0, int channels, int taps, const float* __restrict__ w,
-                                     float* __restrict__ out) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+template <typename T>
+__global__ void hyb_conv_kernel(tha_rows_t rows, tha_state_store_t st, long long conv_state_off, const float* __restrict__ proj,
+                                long long ldp, int col0, int channels, int taps, const float* __restrict__ w, int act, int add_input,
+                                T* __restrict__ out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
-  const int s = rows.row_seq[r], first = rows.seq_first[s];
-  const float* tail = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + conv_state_off + (size_t)c * (taps - 1);
-  float acc = 0.f;
-  for (int j = 0; j < taps; j++) {
-    const int rr = r - (taps - 1 - j);
-    const float x = rr >= first ? proj[(size_t)rr * ldp + col0 + c] : tail[(taps - 1) - (first - rr)];
-    acc = fmaf(w[(size_t)c * taps + j], x, acc);
+  for (int r = blockIdx.y; r < rows.n_rows; r += gridDim.y) {
+    const int s = rows.row_seq[r], first = rows.seq_first[s];
+    const float* tail = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + conv_state_off + (size_t)c * (taps - 1);
+    float acc = 0.f;
+    for (int j = 0; j < taps; j++) {
+      const int rr = r - (taps - 1 - j);
+      const float x = rr >= first ? proj[(size_t)rr * ldp + col0 + c] : tail[(taps - 1) - (first - rr)];
+      acc = fmaf(w[(size_t)c * taps + j], x, acc);
+    }
+    if (act == 1) acc = acc / (1.0f + expf(-acc));
+    if (add_input) acc += proj[(size_t)r * ldp + col0 + c];
+    hyb_store(out + (size_t)r * channels + c, acc);
   }
-  out[(size_t)r * channels + c] = acc / (1.0f + expf(-acc));
 }
 // after the convolution: tail[i] <- the input (taps-1-i) tokens before the end of what the sequence has seen now
 __global__ void hyb_conv_tail_kernel(tha_rows_t rows, tha_state_store_t st, long long conv_state_off, const float* __restrict__ proj,
@@ -1332,6 +1358,7 @@ __device__ __forceinline__ float hyb_act_value(int act, float g, float u, float 
     return p * p;
   }
   if (act == THA_ACT_XIELU) return u > 0.f ? fmaf(limit * u, u, 0.5f * u) : fmaf(alpha, expm1f(u) - u, 0.5f * u);
+  if (act == THA_ACT_SILU_GLU) return g * hyb_sigmoid(g) * u;
   if (act == THA_ACT_GELU_TANH_GLU) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
   const float gc = fminf(g, limit);
   return gc * hyb_sigmoid(alpha * gc) * (fminf(fmaxf(u, -limit), limit) + 1.0f);
@@ -1536,7 +1563,8 @@ extern "C" int tha_hyb_rotary_table(void* stream, const tha_rotary_t* rot, const
 extern "C" int tha_hyb_attn_prepare(void* stream, const tha_attn_t* a, const tha_rows_t* rows, const tha_kv_t* kv, const float* proj,
                                     long long ldp, const float* cos_t, const float* sin_t, int rot_dims, float* q_out) {
   if (rows->n_rows < 1) return THA_STATUS_SUCCESS;
-  if (a->heads % a->kv_heads || rot_dims > a->dim || (rot_dims & 1) || a->kv_heads * a->dim > kv->kv_dim || a->kv_heads * a->vdim > kv->kv_dim)
+  if (a->heads % a->kv_heads || rot_dims > a->dim || (rot_dims & 1) || a->kv_heads * a->dim > kv->kv_dim ||
+      a->kv_heads / (a->v_share > 1 ? a->v_share : 1) * a->vdim > kv->kv_dim)
     return THA_STATUS_INVALID_ARG;
   const int nt = pick_threads(32 * (a->heads + 2 * a->kv_heads));
   THA_CUDA_OK(launch(hyb_attn_prepare_kernel, dim3(rows->n_rows), dim3(nt), 0, (cudaStream_t)stream, false, *a, *rows, *kv, proj, ldp, cos_t,
@@ -1571,11 +1599,12 @@ extern "C" int tha_hyb_attn_gated(void* stream, int dtype, const tha_attn_t* a, 
   const float* gate = (a->head_gate && proj) ? proj + a->o_g : nullptr;
   const long long ldg = ldp;
   if (a->heads % a->kv_heads || a->vdim > 32 * ATT_MAX_VC) return THA_STATUS_NOT_SUPPORTED;
+  if (a->v_share > 1 && (a->kv_heads % a->v_share || a->values_in_keys)) return THA_STATUS_INVALID_ARG;
   const int gsize = a->heads / a->kv_heads;
   // bf16 with heads the tensor-core form covers: 64 pairs per block; else 16 pairs on the fp32 cores
   const bool tc = dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && a->dim % 16 == 0 && a->vdim % 8 == 0 && a->dim <= AM_MAXD && a->vdim <= AM_MAXD &&
                   (a->heads * a->vdim) % 2 == 0;
-  const bool wide = !tc && !gate && !a->head_scale && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && hyb_attn_wide_ok(a);
+  const bool wide = !tc && !gate && !a->head_scale && !a->out_f32 && a->v_share <= 1 && dtype == THA_DT_BF16 && hyb_tc_linear() && hyb_tc_attn() && hyb_attn_wide_ok(a);
   const int pairs = wide ? hyb_attn_wide_pairs(a, rows) : tc ? AM_PAIRS : ATT_PAIRS;
   const int AG = gsize < pairs ? gsize : pairs, AP = pairs / AG;
   const size_t smem = tc ? sizeof(__nv_bfloat16) * ((size_t)ATT_KEYS * (a->dim + 8) + (size_t)ATT_KEYS * (a->vdim + 8))
@@ -1615,7 +1644,10 @@ extern "C" int tha_hyb_attn_gated(void* stream, int dtype, const tha_attn_t* a, 
         THA_CUDA_OK(launch(hyb_attn_kernel<bf16, 16>, grid, dim3(128), smem, s, false, *a, *rows, *kv, q, (bf16*)out, AG, AP, splits, split_scratch, gate, ldg));
       }
     }
-    if (splits > 1)
+    if (splits > 1 && a->out_f32)
+      THA_CUDA_OK(launch(hyb_attn_merge_kernel<float>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (float*)out,
+                         (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits, *a, gate, ldg));
+    else if (splits > 1)
       THA_CUDA_OK(launch(hyb_attn_merge_kernel<bf16>, dim3(ceil_div(rows->n_rows * a->heads, 4)), dim3(128), 0, s, false, (bf16*)out,
                          (const float*)split_scratch, rows->n_rows, a->heads, a->vdim, splits, *a, gate, ldg));
   } else {
@@ -1674,17 +1706,33 @@ extern "C" int tha_hyb_mem_scan(void* stream, int dtype, const tha_mem_t* m, con
   return head_gate_launch(s, (float*)out, o_raw, rows->n_rows, m->heads, m->vdim, m->eps, m->norm, 1, gate, ldp);
 }
 
-extern "C" int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
-                                 const float* proj, long long ldp, int col0, int channels, int taps, const float* w, float* out) {
-  if (rows->n_rows < 1) return THA_STATUS_SUCCESS;
+extern "C" int tha_hyb_conv(void* stream, int dtype, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
+                            const float* proj, long long ldp, int col0, int channels, int taps, const float* w, int act, int add_input,
+                            int out_f32, void* out) {
+  if (rows->n_rows < 1 || channels < 1) return THA_STATUS_SUCCESS;
   if (taps < 1) return THA_STATUS_INVALID_ARG;
   cudaStream_t s = (cudaStream_t)stream;
-  THA_CUDA_OK(launch(hyb_conv_silu_kernel, dim3(ceil_div(channels, 128), rows->n_rows), dim3(128), 0, s, false, *rows, *st, conv_state_off,
-                     proj, ldp, col0, channels, taps, w, out));
-  if (taps > 1)
-    THA_CUDA_OK(launch(hyb_conv_tail_kernel, dim3(ceil_div(channels, 128), rows->n_seqs), dim3(128), 0, s, false, *rows, *st, conv_state_off,
-                       proj, ldp, col0, channels, taps));
+  const dim3 grid(ceil_div(channels, 128), rows->n_rows < 65535 ? rows->n_rows : 65535);
+  if (out_f32 || dtype == THA_DT_F32)
+    THA_CUDA_OK(launch(hyb_conv_kernel<float>, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act,
+                       add_input, (float*)out));
+  else
+    THA_CUDA_OK(launch(hyb_conv_kernel<bf16>, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act,
+                       add_input, (bf16*)out));
   return THA_STATUS_SUCCESS;
+}
+extern "C" int tha_hyb_conv_tail(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
+                                 const float* proj, long long ldp, int col0, int channels, int taps) {
+  if (rows->n_rows < 1 || channels < 1 || taps <= 1) return THA_STATUS_SUCCESS;
+  THA_CUDA_OK(launch(hyb_conv_tail_kernel, dim3(ceil_div(channels, 128), rows->n_seqs), dim3(128), 0, (cudaStream_t)stream, false, *rows, *st,
+                     conv_state_off, proj, ldp, col0, channels, taps));
+  return THA_STATUS_SUCCESS;
+}
+extern "C" int tha_hyb_conv_silu(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,
+                                 const float* proj, long long ldp, int col0, int channels, int taps, const float* w, float* out) {
+  const int status = tha_hyb_conv(stream, THA_DT_F32, rows, st, conv_state_off, proj, ldp, col0, channels, taps, w, 1, 0, 1, out);
+  if (status != THA_STATUS_SUCCESS) return status;
+  return tha_hyb_conv_tail(stream, rows, st, conv_state_off, proj, ldp, col0, channels, taps);
 }
 
 extern "C" int tha_hyb_delta_scan(void* stream, int dtype, const tha_delta_t* d, const tha_rows_t* rows, const tha_state_store_t* st,

@@ -96,6 +96,7 @@ struct Carver {
 struct StepBuffers {
   float *x, *proj, *q, *left, *right, *conv, *dt_raw, *gate_raw, *gu, *down, *sdown, *weight, *oraw, *split; size_t split_floats;
   float *proj2, *qfull, *x0, *sgate;
+  float *xs, *hf, *att;   // the residual streams [rows, n, width]; a normed input before its convolution; fp32 attention maps
   void* sg;
   void *h, *h2, *cq, *qplain, *abuf, *mbuf, *y, *sy, *hn, *hg;
   int *expert_id, *group_off, *sorted_row, *inv;
@@ -112,21 +113,36 @@ static long long hyb_expert_rows() {
   return (v && *v) ? atoll(v) : 1024;
 }
 
+// channels of an attention layer's short convolution: its projected q | k | v columns (q alone when it reads another layer's rows)
+static size_t hyb_attn_conv_channels(const tha_attn_t& a) {
+  size_t c = (size_t)a.heads * a.dim;
+  if (!a.kv_shared) c += (size_t)a.kv_heads * a.dim + (size_t)(a.kv_heads / (a.v_share > 1 ? a.v_share : 1)) * a.vdim;
+  return c;
+}
+
 static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, StepBuffers* b) {
   Carver c{base};
   const size_t W = m->width, es = m->dtype == THA_DT_BF16 ? 2 : 4;
   size_t n_in = 0, qd = 0, av = 0, mv = 0, cc = 0, dd = 0, dg = 0, gu = 0, ff = 0, sff = 0, top = 0, ne = 0;
   size_t n_in2 = 0, qr = 0, qf = 0, qp = 0;
   bool norm2 = false, keep_embed = false;
-  size_t sd = 0;
+  size_t sd = 0, n_str = 0, hfw = 0, attf = 0;
   for (int i = 0; i < m->n_layers; i++) {
     const tha_hyb_layer_t& L = m->layers[i];
     n_in = max(n_in, (size_t)L.n_in);
+    if (L.block == THA_BLOCK_STREAMS) n_str = (size_t)(m->n_streams > 0 ? m->n_streams : 1);
+    if (L.in_conv_taps > 0) hfw = W;
     if (L.pre_add_embed) keep_embed = true;
     sd = max(sd, (size_t)L.side.dim);
     if (L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) {
       qd = max(qd, (size_t)L.attn.heads * L.attn.dim);
       av = max(av, (size_t)L.attn.heads * L.attn.vdim);
+      if (L.attn.diff) attf = max(attf, (size_t)L.attn.heads * L.attn.vdim);
+      if (L.attn.conv_taps > 0) cc = max(cc, hyb_attn_conv_channels(L.attn));
+    }
+    if (L.mixer == THA_MIX_HGRN) {
+      dd = max(dd, (size_t)L.hgrn.heads * L.hgrn.dim);
+      mv = max(mv, (size_t)L.hgrn.heads * L.hgrn.vdim);
     }
     if (L.mixer == THA_MIX_ATTN_GDELTA) {
       dd = max(dd, (size_t)L.gdelta.heads * L.gdelta.dim);
@@ -167,6 +183,9 @@ static size_t carve(const tha_hyb_model_t* m, int R, int n_want, char* base, Ste
   b->x = c.take<float>(R * W);
   b->x0 = c.take<float>(keep_embed ? R * W : 0);
   if (!keep_embed) b->x0 = nullptr;
+  b->xs = c.take<float>(R * n_str * W);
+  b->hf = c.take<float>(R * hfw);
+  b->att = c.take<float>(R * attf);
   b->h = c.take<char>(R * W * es);
   b->proj = c.take<float>(R * n_in);
   b->h2 = c.take<char>(norm2 ? R * W * es : 0);
@@ -218,6 +237,47 @@ typedef __nv_bfloat16 bf16;
     if (_s != THA_STATUS_SUCCESS) return _s; \
   } while (0)
 
+// A mixture's router and chosen experts over R rows of hf (their router logits in fproj): the experts' results land in b.down in
+// expert-sorted order, found per (row, pick) through b.inv and weighted by b.weight by whoever adds them to the residual.
+static int hyb_run_experts(void* stream, HybScratch& sc, int dt, int R, int W, const tha_moe_t& e, const void* hf, const float* fproj,
+                           long long ldf, StepBuffers& b) {
+  cudaStream_t s = (cudaStream_t)stream;
+  const int top = e.top;
+  const bool gated = e.act != THA_ACT_RELU2;
+  const int gw = gated ? 2 * e.ff : e.ff, col_u = gated ? e.ff : 0;   // an expert's rows of w_gate_up; where its up rows start
+  HYB_OK(tha_hyb_moe_route(stream, &e, fproj, ldf, R, b.expert_id, b.weight, b.group_off, b.sorted_row, b.inv));
+  const bool per_expert = dt == THA_DT_BF16 && R >= HYB_EXPERT_LAUNCH_ROWS && (long long)R * top >= hyb_expert_rows() * e.experts &&
+                          e.experts < HYB_HOST_INTS && W % 8 == 0 && e.ff % 8 == 0 && W >= 64 && e.ff >= 64;
+  if (per_expert) {
+    // prompt-sized steps: gather the rows into expert order once, read the group sizes, and give every expert's
+    // contiguous rows to the TMA-fed tcgen05 matmul of the bf16 path (two launches per expert that has rows)
+    if (!sc.host_ints) THA_CUDA_OK(cudaMallocHost((void**)&sc.host_ints, HYB_HOST_INTS * sizeof(int)));
+    THA_CUDA_OK(cudaMemcpyAsync(sc.host_ints, b.group_off, (e.experts + 1) * sizeof(int), cudaMemcpyDeviceToHost, s));
+    THA_CUDA_OK(launch(hyb_gather_rows_kernel<bf16>, dim3(R * top), dim3(128), 0, s, false, (bf16*)b.hg, (const bf16*)hf, (const int*)b.sorted_row, W));
+    THA_CUDA_OK(cudaStreamSynchronize(s));
+    const int* off = sc.host_ints;
+    for (int x = 0; x < e.experts; x++) {
+      const int n = off[x + 1] - off[x];
+      if (n > 0)
+        HYB_OK(tha_hyb_linear(stream, dt, b.gu + (size_t)off[x] * gw, gw, (const bf16*)b.hg + (size_t)off[x] * W, W, 0, nullptr,
+                              (const bf16*)e.w_gate_up + (size_t)x * gw * W, 0, n, gw, W, nullptr, 0));
+    }
+    HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.y, b.gu, gw, 0, col_u, R * top, e.ff, e.limit, e.alpha));
+    for (int x = 0; x < e.experts; x++) {
+      const int n = off[x + 1] - off[x];
+      if (n > 0)
+        HYB_OK(tha_hyb_linear(stream, dt, b.down + (size_t)off[x] * W, W, (const bf16*)b.y + (size_t)off[x] * e.ff, e.ff, 0, nullptr,
+                              (const bf16*)e.w_down + (size_t)x * W * e.ff, 0, n, W, e.ff, nullptr, 0));
+    }
+  } else {
+    HYB_OK(tha_hyb_linear(stream, dt, b.gu, gw, hf, W, 0, b.sorted_row, e.w_gate_up, (long long)gw * W, R * top, gw, W,
+                          b.group_off, e.experts));
+    HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.y, b.gu, gw, 0, col_u, R * top, e.ff, e.limit, e.alpha));
+    HYB_OK(tha_hyb_linear(stream, dt, b.down, W, b.y, e.ff, 0, nullptr, e.w_down, (long long)W * e.ff, R * top, W, e.ff, b.group_off, e.experts));
+  }
+  return THA_STATUS_SUCCESS;
+}
+
 extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_rows_t* rows, const tha_kv_t* kv,
                             const tha_state_store_t* st, int n_want, const int* want_rows, float* logits, float* taps) {
   if (!m || !rows || !kv || !st || m->n_rot > 64) return THA_STATUS_INVALID_ARG;
@@ -255,8 +315,22 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
     const tha_hyb_layer_t& L = m->layers[li];
     const long long ldp = L.n_in;
     const bool seq = L.block == THA_BLOCK_SEQUENTIAL;
-    const bool two_norms = !seq && L.has_norm2 && L.has_ff != THA_FF_NONE;
-    if (seq && h_ready) h_ready = false;
+    const bool streams = L.block == THA_BLOCK_STREAMS;
+    const int n_str = m->n_streams > 0 ? m->n_streams : 1;
+    const bool two_norms = !seq && !streams && L.has_norm2 && L.has_ff != THA_FF_NONE;
+    if (streams) {
+      // the mixer's input: the first sublayer's read of the streams and its norm (left behind by the previous layer's last
+      // pass, or made here from the embedding output), then h + conv(h) continuing from the slot's tail
+      const bool conv = L.in_conv_taps > 0;
+      if (!h_ready)
+        HYB_OK(tha_hyb_streams(stream, dt, b.xs, n_str, (li == 0 || m->layers[li - 1].block != THA_BLOCK_STREAMS) ? b.x : nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr,
+                               nullptr, &L.streams1, &L.norm1, m->eps, conv, conv ? (void*)b.hf : b.h, R, W));
+      h_ready = false;
+      if (conv) {
+        HYB_OK(tha_hyb_conv(stream, dt, rows, st, L.in_conv_state_off, b.hf, W, 0, W, L.in_conv_taps, L.in_conv_w, 0, 1, 0, b.h));
+        HYB_OK(tha_hyb_conv_tail(stream, rows, st, L.in_conv_state_off, b.hf, W, 0, W, L.in_conv_taps));
+      }
+    } else if (seq && h_ready) h_ready = false;
     else if (seq && (L.pre_add_embed || L.pre_vec))   // a pass's re-entry addends and the mixer's norm in one pass over x
       HYB_OK(tha_hyb_add_norm(stream, dt, b.x, nullptr, 0.f, nullptr, 0.f, L.pre_add_embed ? b.x0 : nullptr, L.pre_vec, &L.norm1, m->eps, b.h, R, W));
     else if (two_norms) HYB_OK(tha_hyb_norm_pair(stream, dt, b.h, b.h2, b.x, &L.norm1, &L.norm2, m->eps, R, W));
@@ -266,10 +340,29 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
     if (L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) {
       const tha_attn_t& a = L.attn;
       const int rd = a.rot >= 0 ? m->rot[a.rot].dims : 0;
-      HYB_OK(tha_hyb_attn_prepare(stream, &a, rows, kv, b.proj, ldp, a.rot >= 0 ? b.cos_t[a.rot] : nullptr,
+      // a short convolution over the projected q | k | v: the rest of the layer reads the convolved copy
+      tha_attn_t ap = a;
+      const float* pq = b.proj;
+      long long ldq = ldp;
+      if (a.conv_taps > 0) {
+        const int C = (int)hyb_attn_conv_channels(a);
+        HYB_OK(tha_hyb_conv(stream, dt, rows, st, a.conv_state_off, b.proj, ldp, a.o_q, C, a.conv_taps, a.conv_w, 0, 0, 1, b.conv));
+        HYB_OK(tha_hyb_conv_tail(stream, rows, st, a.conv_state_off, b.proj, ldp, a.o_q, C, a.conv_taps));
+        ap.o_q = 0; ap.o_k = a.heads * a.dim; ap.o_v = ap.o_k + a.kv_heads * a.dim;
+        pq = b.conv; ldq = C;
+      }
+      HYB_OK(tha_hyb_attn_prepare(stream, &ap, rows, kv, pq, ldq, a.rot >= 0 ? b.cos_t[a.rot] : nullptr,
                                   a.rot >= 0 ? b.sin_t[a.rot] : nullptr, rd, b.q));
-      HYB_OK(tha_hyb_attn_gated(stream, dt, &a, rows, kv, b.q, b.abuf, b.split_floats ? b.split : nullptr, b.split_floats, b.proj, ldp));
-      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.abuf, a.heads * a.vdim, 0, nullptr, a.w_o, 0, R, W, a.heads * a.vdim, nullptr, 0));
+      int ov = a.heads * a.vdim;   // columns of the mixer's result before its output matrix
+      if (a.diff) {
+        // two maps per head as fp32, then their combination, the head norm and the gate
+        HYB_OK(tha_hyb_attn_gated(stream, dt, &a, rows, kv, b.q, b.att, b.split_floats ? b.split : nullptr, b.split_floats, nullptr, 0));
+        HYB_OK(tha_hyb_diff_combine(stream, dt, &a, b.att, b.proj, ldp, b.abuf, R));
+        ov = a.heads / 2 * a.vdim;
+      } else {
+        HYB_OK(tha_hyb_attn_gated(stream, dt, &a, rows, kv, b.q, b.abuf, b.split_floats ? b.split : nullptr, b.split_floats, b.proj, ldp));
+      }
+      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.abuf, ov, 0, nullptr, a.w_o, 0, R, W, ov, nullptr, 0));
       if (L.mixer == THA_MIX_ATTN_GDELTA) {
         const tha_gdelta_t& g = L.gdelta;
         HYB_OK(tha_hyb_gdelta_scan(stream, dt, &g, rows, st, b.proj, ldp, b.dt_raw, b.oraw, b.mbuf));
@@ -299,6 +392,10 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       const tha_gla_t& g = L.gla;
       HYB_OK(tha_hyb_linear(stream, dt, b.dt_raw, g.heads * g.dim, b.proj + g.o_a1, ldp, 1, nullptr, g.w_a2, 0, R, g.heads * g.dim, g.rank, nullptr, 0));
       HYB_OK(tha_hyb_gla_scan(stream, dt, &g, rows, st, b.proj, ldp, b.dt_raw, b.oraw, b.mbuf));
+      HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, g.heads * g.vdim, 0, nullptr, g.w_o, 0, R, W, g.heads * g.vdim, nullptr, 0));
+    } else if (L.mixer == THA_MIX_HGRN) {
+      const tha_hgrn_t& g = L.hgrn;
+      HYB_OK(tha_hyb_hgrn_scan(stream, dt, &g, rows, st, b.proj, ldp, b.dt_raw, b.oraw, b.mbuf));
       HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, g.heads * g.vdim, 0, nullptr, g.w_o, 0, R, W, g.heads * g.vdim, nullptr, 0));
     } else if (L.mixer == THA_MIX_LATENT) {
       const tha_latent_t& a = L.latent;
@@ -332,6 +429,40 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
       HYB_OK(tha_hyb_linear(stream, dt, b.left, W, b.mbuf, a.heads * a.vdim, 0, nullptr, a.w_o, 0, R, W, a.heads * a.vdim, nullptr, 0));
     } else {
       return THA_STATUS_NOT_SUPPORTED;
+    }
+    if (streams) {
+      // what follows the layer: the tap, the sum of the streams for the final norm, or the next layer's first read
+      const tha_hyb_layer_t* next = li + 1 < m->n_layers && m->layers[li + 1].block == THA_BLOCK_STREAMS ? &m->layers[li + 1] : nullptr;
+      float* tap = taps ? taps + (size_t)li * R * W : (float*)nullptr;
+      float* sum_out = next ? (float*)nullptr : b.x;
+      const bool nconv = next && next->in_conv_taps > 0;
+      void* nout = next ? (nconv ? (void*)b.hf : b.h) : nullptr;
+      if (L.has_ff == THA_FF_NONE) {
+        HYB_OK(tha_hyb_streams(stream, dt, b.xs, n_str, nullptr, &L.streams1, b.left, nullptr, 0, nullptr, nullptr, nullptr, tap, sum_out,
+                               next ? &next->streams1 : nullptr, next ? &next->norm1 : nullptr, m->eps, nconv, nout, R, W));
+      } else {
+        // the mixer's write and the feed-forward's read in one pass over the streams
+        HYB_OK(tha_hyb_streams(stream, dt, b.xs, n_str, nullptr, &L.streams1, b.left, nullptr, 0, nullptr, nullptr, nullptr, nullptr, nullptr,
+                               &L.streams2, &L.norm2, m->eps, 0, b.h2, R, W));
+        HYB_OK(tha_hyb_linear(stream, dt, b.proj2, L.n_in2, b.h2, W, 0, nullptr, L.w_in2, 0, R, L.n_in2, W, nullptr, 0));
+        if (L.has_ff == THA_FF_DENSE) {
+          const tha_dense_ff_t& d = L.dense;
+          if (d.act == THA_ACT_POLYNORM) HYB_OK(tha_hyb_polynorm(stream, dt, b.sy, b.proj2, L.n_in2, d.o_up, d.b_up, d.act_c, m->eps, R, d.ff));
+          else if (d.b_up) return THA_STATUS_NOT_SUPPORTED;
+          else HYB_OK(tha_hyb_ff_act(stream, dt, d.act, b.sy, b.proj2, L.n_in2, d.o_gate, d.o_up, R, d.ff, d.act_p, d.act_q));
+          HYB_OK(tha_hyb_linear(stream, dt, b.sdown, W, b.sy, d.ff, 0, nullptr, d.w_down, 0, R, W, d.ff, nullptr, 0));
+          HYB_OK(tha_hyb_streams(stream, dt, b.xs, n_str, nullptr, &L.streams2, b.sdown, d.b_down, 0, nullptr, nullptr, nullptr, tap, sum_out,
+                                 next ? &next->streams1 : nullptr, next ? &next->norm1 : nullptr, m->eps, nconv, nout, R, W));
+        } else {
+          const tha_moe_t& e = L.moe;
+          if (e.shared_ff > 0) return THA_STATUS_NOT_SUPPORTED;
+          HYB_OK(hyb_run_experts(stream, sc, dt, R, W, e, b.h2, b.proj2, L.n_in2, b));
+          HYB_OK(tha_hyb_streams(stream, dt, b.xs, n_str, nullptr, &L.streams2, nullptr, nullptr, e.top, b.weight, b.inv, b.down, tap, sum_out,
+                                 next ? &next->streams1 : nullptr, next ? &next->norm1 : nullptr, m->eps, nconv, nout, R, W));
+        }
+      }
+      h_ready = next != nullptr;
+      continue;
     }
     if (seq) {
       // x += m * mixer and the feed-forward's norm of the new x in one pass; the feed-forward; then its residual add, the
@@ -390,38 +521,7 @@ extern "C" int tha_hyb_step(void* stream, const tha_hyb_model_t* m, const tha_ro
     } else if (L.has_ff == THA_FF_MOE) {
       const tha_moe_t& e = L.moe;
       top = e.top;
-      const bool gated = e.act != THA_ACT_RELU2;
-      const int gw = gated ? 2 * e.ff : e.ff, col_u = gated ? e.ff : 0;   // an expert's rows of w_gate_up; where its up rows start
-      HYB_OK(tha_hyb_moe_route(stream, &e, fproj, ldf, R, b.expert_id, b.weight, b.group_off, b.sorted_row, b.inv));
-      const bool per_expert = dt == THA_DT_BF16 && R >= HYB_EXPERT_LAUNCH_ROWS && (long long)R * top >= hyb_expert_rows() * e.experts &&
-                              e.experts < HYB_HOST_INTS && W % 8 == 0 && e.ff % 8 == 0 && W >= 64 && e.ff >= 64;
-      if (per_expert) {
-        // prompt-sized steps: gather the rows into expert order once, read the group sizes, and give every expert's
-        // contiguous rows to the TMA-fed tcgen05 matmul of the bf16 path (two launches per expert that has rows)
-        if (!sc.host_ints) THA_CUDA_OK(cudaMallocHost((void**)&sc.host_ints, HYB_HOST_INTS * sizeof(int)));
-        THA_CUDA_OK(cudaMemcpyAsync(sc.host_ints, b.group_off, (e.experts + 1) * sizeof(int), cudaMemcpyDeviceToHost, s));
-        THA_CUDA_OK(launch(hyb_gather_rows_kernel<bf16>, dim3(R * top), dim3(128), 0, s, false, (bf16*)b.hg, (const bf16*)hf, (const int*)b.sorted_row, W));
-        THA_CUDA_OK(cudaStreamSynchronize(s));
-        const int* off = sc.host_ints;
-        for (int x = 0; x < e.experts; x++) {
-          const int n = off[x + 1] - off[x];
-          if (n > 0)
-            HYB_OK(tha_hyb_linear(stream, dt, b.gu + (size_t)off[x] * gw, gw, (const bf16*)b.hg + (size_t)off[x] * W, W, 0, nullptr,
-                                  (const bf16*)e.w_gate_up + (size_t)x * gw * W, 0, n, gw, W, nullptr, 0));
-        }
-        HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.y, b.gu, gw, 0, col_u, R * top, e.ff, e.limit, e.alpha));
-        for (int x = 0; x < e.experts; x++) {
-          const int n = off[x + 1] - off[x];
-          if (n > 0)
-            HYB_OK(tha_hyb_linear(stream, dt, b.down + (size_t)off[x] * W, W, (const bf16*)b.y + (size_t)off[x] * e.ff, e.ff, 0, nullptr,
-                                  (const bf16*)e.w_down + (size_t)x * W * e.ff, 0, n, W, e.ff, nullptr, 0));
-        }
-      } else {
-        HYB_OK(tha_hyb_linear(stream, dt, b.gu, gw, hf, W, 0, b.sorted_row, e.w_gate_up, (long long)gw * W, R * top, gw, W,
-                              b.group_off, e.experts));
-        HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.y, b.gu, gw, 0, col_u, R * top, e.ff, e.limit, e.alpha));
-        HYB_OK(tha_hyb_linear(stream, dt, b.down, W, b.y, e.ff, 0, nullptr, e.w_down, (long long)W * e.ff, R * top, W, e.ff, b.group_off, e.experts));
-      }
+      HYB_OK(hyb_run_experts(stream, sc, dt, R, W, e, hf, fproj, ldf, b));
       if (e.shared_ff > 0) {
         HYB_OK(tha_hyb_ff_act(stream, dt, e.act, b.sy, fproj, ldf, e.o_sgate, e.o_sup, R, e.shared_ff, e.shared_limit, e.alpha));
         HYB_OK(tha_hyb_linear(stream, dt, b.sdown, W, b.sy, e.shared_ff, 0, nullptr, e.w_sdown, 0, R, W, e.shared_ff, nullptr, 0));

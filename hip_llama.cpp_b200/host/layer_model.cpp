@@ -17,6 +17,7 @@
 void register_timerax();   // host/arch_timerax.cpp
 void register_numizen();   // host/arch_numizen.cpp
 void register_bozovik();   // host/arch_bozovik.cpp
+void register_mozetar();   // host/arch_mozetar.cpp
 
 // ---- registry -----------------------------------------------------------------------------------------------------
 static std::vector<ArchitectureEntry>& registry() {
@@ -30,6 +31,7 @@ static void register_builtin() {
     register_timerax();
     register_numizen();
     register_bozovik();
+    register_mozetar();
   });
 }
 void register_architecture(const ArchitectureEntry& e) {
@@ -182,13 +184,23 @@ struct Stack {
   int rows = 0;
   Stack(const SafeTensors& file_, int dtype_, int cols_) : file(file_), dtype(dtype_), cols(cols_) {}
   // returns the first row of the added matrix; checks [rows_expected, cols]
-  int add(const std::string& name, long long rows_expected) {
+  int add(const std::string& name, long long rows_expected, const std::vector<int>* order = nullptr) {
     const TensorInfo& t = file.info(name);
     const long long r = t.shape.size() == 2 ? t.shape[0] : -1, c = t.shape.size() == 2 ? t.shape[1] : -1;
     if (r != rows_expected || c != cols)
       throw std::runtime_error("tensor '" + name + "': shape [" + std::to_string(r) + ", " + std::to_string(c) + "] where [" +
                                std::to_string(rows_expected) + ", " + std::to_string(cols) + "] is expected");
     if (dtype == THA_DT_BF16) file.read_bf16(name, &h); else file.read_f32(name, &f);
+    if (order) {   // row i of the stack is row (*order)[i] of the tensor
+      const size_t n = (size_t)r * cols;
+      if (dtype == THA_DT_BF16) {
+        std::vector<uint16_t> src(h.end() - n, h.end());
+        for (long long i = 0; i < r; i++) memcpy(h.data() + h.size() - n + (size_t)i * cols, src.data() + (size_t)(*order)[i] * cols, (size_t)cols * 2);
+      } else {
+        std::vector<float> src(f.end() - n, f.end());
+        for (long long i = 0; i < r; i++) memcpy(f.data() + f.size() - n + (size_t)i * cols, src.data() + (size_t)(*order)[i] * cols, (size_t)cols * 4);
+      }
+    }
     const int at = rows;
     rows += (int)r;
     return at;
@@ -236,7 +248,7 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       tha_norm_t n = {};
       n.kind = spec.norm_kind;
       n.w = vec(name, W);
-      n.w_offset = 1.0f;
+      n.w_offset = spec.norm_w_offset;
       if (spec.norm_kind == THA_NORM_LAYER) {
         n.w_offset = 0.0f;
         n.b = vec(name + ".b", W);
@@ -269,6 +281,16 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
           }
           mag = (float)(0.1 * log(rs.factor) + 1.0);
         }
+        if (rs.by_wavelength) {
+          if (!(rs.high > rs.low) || !(rs.factor > 0.0) || !(rs.original > 0.0)) throw std::runtime_error("rotary scaling: needs high > low, factor > 0, original > 0");
+          for (int i = 0; i < half; i++) {
+            const double l = 2.0 * M_PI / f[i];
+            if (l < rs.original / rs.high) continue;
+            if (l > rs.original / rs.low) { f[i] = f[i] / rs.factor; continue; }
+            const double t = (rs.original / l - rs.low) / (rs.high - rs.low);
+            f[i] = (1.0 - t) * f[i] / rs.factor + t * f[i];
+          }
+        }
         tha_rotary_t R;
         R.inv_freq = (const double*)m->upload(f.data(), f.size() * 8);
         R.dims = dims;
@@ -278,6 +300,9 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       }
       return (int)r;
     };
+    long long state = 0;
+    size_t li_now = 0;
+    m->layers_.resize(spec.layers.size());
     // softmax attention (alone, or as one side of a two-sided mixer): its matrices into the stack, its options
     auto attention = [&](const AttnSpec& a, Stack& in, tha_attn_t& A) {
       if (a.heads < 1 || a.kv_heads < 1 || a.heads % a.kv_heads) throw std::runtime_error("attention: heads must be a multiple of kv_heads");
@@ -293,16 +318,67 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         A.rot = rotary(a.rot);
         A.rot_layout = a.rot.halves ? THA_ROT_HALVES : THA_ROT_INTERLEAVED;
       }
-      A.cache_layer = m->n_cache_layers_++;
+      const int maps = a.diff ? 2 : 1;   // score maps per head: a differential head owns two query rows and two key rows
+      A.heads = a.heads * maps; A.kv_heads = a.kv_heads * maps;
+      const long long cq = (long long)A.heads * a.dim, ck = (long long)A.kv_heads * a.dim, cv = (long long)a.kv_heads * a.vdim;
       m->separate_values_ = true;
-      m->kv_dim_ = std::max(m->kv_dim_, std::max(a.kv_heads * a.dim, a.kv_heads * a.vdim));
-      A.o_q = in.add(a.q, (long long)a.heads * a.dim);
-      A.o_k = in.add(a.k, (long long)a.kv_heads * a.dim);
-      A.o_v = in.add(a.v, (long long)a.kv_heads * a.vdim);
+      if (a.kv_from >= 0) {
+        // the rows of an earlier layer: same head counts and rotation, nothing of its own in the cache
+        if ((size_t)a.kv_from >= li_now || spec.layers[a.kv_from].same_weights_as >= 0) throw std::runtime_error("attention: 'kv_from' must name an earlier layer");
+        const LayerSpec& d = spec.layers[a.kv_from];
+        if ((d.mixer != THA_MIX_ATTN) || d.attn.kv_from >= 0 || d.attn.kv_heads != a.kv_heads || d.attn.dim != a.dim || d.attn.vdim != a.vdim ||
+            d.attn.diff != a.diff)
+          throw std::runtime_error("attention: the layer named by 'kv_from' does not hold rows of this layer's shape");
+        A.kv_shared = 1;
+        A.cache_layer = m->layers_[a.kv_from].attn.cache_layer;
+      } else {
+        A.cache_layer = m->n_cache_layers_++;
+        m->kv_dim_ = std::max(m->kv_dim_, (int)std::max(ck, cv));
+      }
+      if (a.diff) {
+        // the q rows, stored head by head as [first map | second map], reordered per key/value group as [first maps of the
+        // group's heads | second maps]: query map j then reads key head j / (heads / kv_heads), as grouped attention does
+        const int gs = a.heads / a.kv_heads;
+        std::vector<int> order((size_t)cq);
+        for (int h = 0; h < a.heads; h++)
+          for (int mp = 0; mp < 2; mp++)
+            for (int d = 0; d < a.dim; d++)
+              order[(size_t)(((h / gs) * 2 + mp) * gs + h % gs) * a.dim + d] = (h * 2 + mp) * a.dim + d;
+        A.o_q = in.add(a.q, cq, &order);
+        A.diff = 1; A.v_share = 2; A.out_f32 = 1;
+        double d1 = 0.0, d2 = 0.0;
+        std::vector<float> l1, k1, l2, k2;
+        file.read_f32(a.lq1, &l1); file.read_f32(a.lk1, &k1); file.read_f32(a.lq2, &l2); file.read_f32(a.lk2, &k2);
+        if ((int)l1.size() != a.dim || (int)k1.size() != a.dim || (int)l2.size() != a.dim || (int)k2.size() != a.dim)
+          throw std::runtime_error("differential attention: the four lambda vectors must have `dim` entries");
+        for (int d = 0; d < a.dim; d++) { d1 += (double)l1[d] * k1[d]; d2 += (double)l2[d] * k2[d]; }
+        A.diff_lambda = (float)(exp(d1) - exp(d2) + (double)a.diff_init);
+        A.diff_mult = 1.0f - a.diff_init;
+      } else {
+        A.o_q = in.add(a.q, cq);
+      }
+      if (a.kv_from < 0) {
+        A.o_k = in.add(a.k, ck);
+        A.o_v = in.add(a.v, cv);
+      }
+      A.q_temp_coef = a.q_temp_coef; A.q_temp_every = a.q_temp_every > 0 ? a.q_temp_every : 0;
+      if (a.conv_taps > 0) {
+        if (a.diff) throw std::runtime_error("attention: a short convolution behind differential projections is not served");
+        std::vector<float> taps;
+        file.read_f32(a.q + ".conv", &taps);
+        if (a.kv_from < 0) { file.read_f32(a.k + ".conv", &taps); file.read_f32(a.v + ".conv", &taps); }
+        const long long C = cq + (a.kv_from < 0 ? ck + cv : 0);
+        if ((long long)taps.size() != C * a.conv_taps) throw std::runtime_error("attention: convolution taps do not fit [channels, " + std::to_string(a.conv_taps) + "]");
+        A.conv_taps = a.conv_taps;
+        A.conv_w = (const float*)m->upload(taps.data(), taps.size() * 4);
+        A.conv_state_off = state;
+        state += C * (a.conv_taps - 1);
+      }
       if (!a.g.empty()) { A.head_gate = 1; A.o_g = in.add(a.g, a.heads); }
       if (!a.sink.empty()) A.sink = vec(a.sink, a.heads);
       else if (a.sink_zero) { std::vector<float> z(a.heads, 0.f); A.sink = (const float*)m->upload(z.data(), z.size() * 4); }
       if (!a.temp.empty()) A.head_scale = vec(a.temp, a.heads);
+      if (a.diff && (A.sink || A.head_scale)) throw std::runtime_error("differential attention: sinks and per-head factors are not served");
       A.w_o = mat(a.o, W, a.heads * a.vdim);
     };
     // row `row` of a [rows, width] tensor as an fp32 device vector (uploaded once per tensor)
@@ -319,9 +395,8 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       }
       return it->second + (size_t)row * W;
     };
-    m->layers_.resize(spec.layers.size());
-    long long state = 0;
     for (size_t li = 0; li < spec.layers.size(); li++) {
+      li_now = li;
       const LayerSpec& ls = spec.layers[li];
       tha_hyb_layer_t& L = m->layers_[li];
       if (ls.same_weights_as >= 0) {
@@ -331,6 +406,13 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         L.pre_add_embed = ls.pre_add_embed ? 1 : 0;
         L.pre_vec = nullptr;
         if (!ls.pre_vec.empty()) L.pre_vec = pre_vector(ls.pre_vec, ls.pre_vec_row);
+        if (L.in_conv_taps > 1) { L.in_conv_state_off = state; state += (long long)W * (L.in_conv_taps - 1); }
+        if (L.mixer == THA_MIX_HGRN) {
+          L.hgrn.state_off = state;
+          state += (long long)L.hgrn.heads * L.hgrn.dim * ((L.hgrn.vdim + 7) / 8 * 8);
+        }
+        if ((L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) && (L.attn.kv_shared || L.attn.conv_taps > 0))
+          throw std::runtime_error("a repeated attention layer with a short convolution or another layer's cache rows is not served");
         if (L.mixer == THA_MIX_ATTN || L.mixer == THA_MIX_ATTN_GDELTA) {
           L.attn.cache_layer = m->n_cache_layers_++;
           if (L.mixer == THA_MIX_ATTN_GDELTA) {
@@ -363,6 +445,25 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
       if (ls.block == THA_BLOCK_SEQUENTIAL && ls.has_ff && (ls.ff_kind != THA_FF_DENSE || ls.norm2.empty()))
         throw std::runtime_error("a sequential block serves a dense feed-forward behind a second norm, or none");
       L.norm1 = norm(ls.norm1);
+      if (ls.block == THA_BLOCK_STREAMS) {
+        const int n = spec.n_streams;
+        if (n < 1 || n > 16) throw std::runtime_error("residual streams: 1 to 16 streams are served");
+        if (spec.norm_kind != THA_NORM_RMS) throw std::runtime_error("residual streams are served with rms norms");
+        if (ls.has_ff && ls.norm2.empty()) throw std::runtime_error("residual streams: the feed-forward needs a norm of its own");
+        auto weights = [&](const StreamsSpec& w, tha_streams_t* out) {
+          out->in = vec(w.in, n); out->out = vec(w.out, n); out->mix = vec(w.mix, (size_t)n * n);
+        };
+        weights(ls.streams1, &L.streams1);
+        if (ls.has_ff) weights(ls.streams2, &L.streams2);
+      }
+      if (!ls.in_conv.empty()) {
+        if (ls.block != THA_BLOCK_STREAMS) throw std::runtime_error("a convolution of the mixer's input is served in stream blocks");
+        if (ls.in_conv_taps < 1) throw std::runtime_error("the input convolution needs at least one tap");
+        L.in_conv_taps = ls.in_conv_taps;
+        L.in_conv_w = vec(ls.in_conv, (size_t)W * ls.in_conv_taps);
+        L.in_conv_state_off = state;
+        state += (long long)W * (ls.in_conv_taps - 1);
+      }
       if (!ls.scale_mix.empty()) L.scale_mix = vec(ls.scale_mix, W);
       if (!ls.scale_ff.empty() && ls.has_ff) L.scale_ff = vec(ls.scale_ff, W);
       Stack in(file, dtype, W);
@@ -468,6 +569,21 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         G.w_o = mat(g.o, W, g.heads * g.vdim);
         G.state_off = state;
         state += (long long)g.heads * g.dim * ((g.vdim + 7) / 8 * 8);   // value columns padded to eights
+      } else if (ls.mixer == THA_MIX_HGRN) {
+        const HgrnSpec& g = ls.hgrn;
+        if (g.heads < 1 || g.dim < 1 || g.vdim < 1) throw std::runtime_error("gated linear recurrence: heads, dim and vdim must be positive");
+        if (g.dim > 512) throw std::runtime_error("gated linear recurrence: more than 512 key channels per head are not served");
+        tha_hgrn_t& G = L.hgrn;
+        G.heads = g.heads; G.dim = g.dim; G.vdim = g.vdim; G.eps = spec.eps;
+        G.o_q = in.add(g.q, (long long)g.heads * g.dim);
+        G.o_f = in.add(g.f, (long long)g.heads * g.dim);
+        G.o_v = in.add(g.v, (long long)g.heads * g.vdim);
+        G.f_b = vec(g.f_b, (size_t)g.heads * g.dim);
+        G.lower = vec(g.lower, (size_t)g.heads * g.dim);
+        G.norm = vec(g.norm, g.vdim);
+        G.w_o = mat(g.o, W, g.heads * g.vdim);
+        G.state_off = state;
+        state += (long long)g.heads * g.dim * ((g.vdim + 7) / 8 * 8);   // value columns padded to eights, as for gated linear attention
       } else if (ls.mixer == THA_MIX_LATENT) {
         const LatentSpec& a = ls.latent;
         const bool direct_q = !a.q.empty();
@@ -537,9 +653,19 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         if (d.ff < 1) throw std::runtime_error("dense feed-forward: ff must be positive");
         L.dense.ff = d.ff;
         L.dense.act = d.act;
-        if (d.act != THA_ACT_RELU2 && d.act != THA_ACT_XIELU) L.dense.o_gate = fin.add(d.gate, d.ff);
+        if (d.act != THA_ACT_RELU2 && d.act != THA_ACT_XIELU && d.act != THA_ACT_POLYNORM) L.dense.o_gate = fin.add(d.gate, d.ff);
         L.dense.o_up = fin.add(d.up, d.ff);
         L.dense.w_down = mat(d.down, W, d.ff);
+        if ((!d.up_b.empty() || !d.down_b.empty() || d.act == THA_ACT_POLYNORM) && ls.block != THA_BLOCK_STREAMS)
+          throw std::runtime_error("dense feed-forward: biases and the PolyNorm activation are served in stream blocks");
+        if (!d.up_b.empty()) L.dense.b_up = vec(d.up_b, d.ff);
+        if (!d.down_b.empty()) L.dense.b_down = vec(d.down_b, W);
+        if (d.act == THA_ACT_POLYNORM) {
+          std::vector<float> c;
+          file.read_f32(d.act_params, &c);
+          if (c.size() != 4) throw std::runtime_error("tensor '" + d.act_params + "' must hold four numbers");
+          for (int i = 0; i < 4; i++) L.dense.act_c[i] = c[i];
+        }
         if (d.act == THA_ACT_XIELU) {
           std::vector<float> pq;
           file.read_f32(d.act_params, &pq);
@@ -606,6 +732,7 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
     M.logit_softcap = spec.logit_softcap;
     M.embed = mat(spec.embed, spec.vocab, W);
     M.embed_scale = spec.embed_scale;
+    M.n_streams = spec.n_streams;
     if (!spec.side_table.empty()) {
       if (spec.side_cols < 1) throw std::runtime_error("a side table needs its number of columns");
       M.side_table = mat(spec.side_table, spec.vocab, spec.side_cols);

@@ -23,9 +23,13 @@ struct RotarySpec {
   bool halves = false;        // pairs (i, i + dims / 2) instead of (2i, 2i + 1); the table is the same, the kernels pair by it
   bool yarn = false;          // frequency interpolation between a fast and a slow wavelength bound
   double factor = 1.0, original = 0.0, fast = 32.0, slow = 1.0;
+  // stretch by wavelength l = 2 pi / f against the original context: f kept where l < original / high, f / factor where
+  // l > original / low, between them (1 - s) f / factor + s f with s = (original / l - low) / (high - low); amplitude 1
+  bool by_wavelength = false;
+  double low = 1.0, high = 4.0;
   bool operator==(const RotarySpec& o) const {
     return dims == o.dims && base == o.base && yarn == o.yarn && factor == o.factor && original == o.original && fast == o.fast &&
-           slow == o.slow;
+           slow == o.slow && by_wavelength == o.by_wavelength && low == o.low && high == o.high;
   }
 };
 struct AttnSpec {
@@ -40,6 +44,23 @@ struct AttnSpec {
   std::string temp;                      // [heads] per-head factor on the scores; empty: none
   std::string g;                         // [heads, width] one sigmoid output gate per head; empty: none
   bool fp32_scores = false;              // scores and softmax weights stay fp32 in every number format
+  // differential attention: q holds heads x 2 x dim rows and k kv_heads x 2 x dim rows ([first map | second map] per head), both
+  // maps read the same values; o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff_init, then o / rms(o)
+  // times (1 - diff_init) and the head's gate
+  bool diff = false;
+  float diff_init = 0.f;
+  std::string lq1, lk1, lq2, lk2;        // [dim] each
+  float q_temp_coef = 0.f;               // q_temp_every > 0: queries times 1 + coef * ln(floor((p + 1) / every) + 1)
+  int q_temp_every = 0;
+  int conv_taps = 0;                     // > 0: a short causal convolution behind the q, k and v projections ("<tensor>.conv")
+  int kv_from = -1;                      // >= 0: no key / value tensors; the layer reads the cache rows of that layer (index into `layers`)
+};
+struct HgrnSpec {
+  int heads = 0, dim = 0, vdim = 0;
+  std::string q, f, f_b, lower, v, norm, o;
+};
+struct StreamsSpec {
+  std::string in, out, mix;              // [n], [n], [n, n]
 };
 struct GDeltaSpec {
   int heads = 0, dim = 0;
@@ -77,7 +98,8 @@ struct LatentSpec {
 struct DenseSpec {
   int ff = 0, act = THA_ACT_GELU_TANH_GLU;
   std::string gate, up, down;            // ungated activations have no `gate`
-  std::string act_params;                // THA_ACT_XIELU: [2]
+  std::string act_params;                // THA_ACT_XIELU: [2]; THA_ACT_POLYNORM: [4]
+  std::string up_b, down_b;              // biases; empty: none
 };
 struct MoeSpec {
   int experts = 0, top = 0, ff = 0, shared_ff = 0;
@@ -115,6 +137,10 @@ struct LayerSpec {
   int pre_vec_row = 0;
   bool has_ff = false;
   MoeSpec moe;
+  HgrnSpec hgrn;                         // THA_MIX_HGRN
+  StreamsSpec streams1, streams2;        // THA_BLOCK_STREAMS
+  std::string in_conv;                   // [width, taps]: the mixer's normed input h becomes h + conv(h); empty: none
+  int in_conv_taps = 0;
 };
 struct LayerProgramSpec {
   int width = 0, vocab = 0;
@@ -122,6 +148,8 @@ struct LayerProgramSpec {
   // every norm over the width (the layers' and the final one): THA_NORM_RMS with weights stored around zero, or
   // THA_NORM_DYT with "<name>.alpha" (a scalar) and "<name>.b" beside the weight
   int norm_kind = THA_NORM_RMS;
+  float norm_w_offset = 1.0f;            // THA_NORM_RMS: what is added to the stored weight (0: the weight is stored as it is used)
+  int n_streams = 0;                     // THA_BLOCK_STREAMS layers: copies of the residual
   float embed_scale = 1.0f;
   std::string side_table;                // [vocab, side_cols]: per-token side inputs, a column range per layer; empty: none
   int side_cols = 0;

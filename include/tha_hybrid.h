@@ -36,9 +36,11 @@ extern "C" {
 #define THA_MIX_LATENT 3   /* softmax attention whose keys and values are expanded from one cached low-rank latent */
 #define THA_MIX_ATTN 4     /* softmax attention alone (tha_attn_t with its window, sink, per-head scale and gate options) */
 #define THA_MIX_ATTN_GDELTA 5 /* softmax attention and a generalized delta rule side by side: mix_left * left + mix_right * right */
+#define THA_MIX_HGRN 6     /* gated linear recurrence whose forget gate also decides what is written (tha_hgrn_t) */
 
 #define THA_BLOCK_PARALLEL 0   /* x <- x + mixer(norm1 x) + ff(norm x): mixer and feed-forward read the same x */
 #define THA_BLOCK_SEQUENTIAL 1 /* x <- x + m mixer(norm1 x), then x <- x + m ff(norm2 x), then the per-token side input */
+#define THA_BLOCK_STREAMS 2    /* several residual streams: every sublayer reads a weighted sum of them and writes to all (tha_streams_t) */
 
 #define THA_NORM_RMS 0     /* x / sqrt(mean(x^2) + eps) * (w_offset + w) */
 #define THA_NORM_DYT 1     /* tanh(alpha * x) * w + b: element-wise, no statistics */
@@ -53,6 +55,9 @@ extern "C" {
 #define THA_ACT_RELU2 1       /* max(u, 0)^2, no gate */
 #define THA_ACT_GELU_TANH_GLU 2 /* gelu(g) u, gelu in its tanh form */
 #define THA_ACT_XIELU 3       /* no gate; z > 0: softplus(p) z^2 + z / 2; z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z / 2 */
+#define THA_ACT_SILU_GLU 4    /* g sigmoid(g) u */
+#define THA_ACT_POLYNORM 5    /* no gate; over a row z: c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3, N(v) = v / sqrt(mean(v^2) + eps), powers by element
+                                 (a reduction over the row: tha_hyb_polynorm) */
 
 #define THA_ROUTE_TOPK_SOFTMAX 0    /* the top logits, softmax over the chosen */
 #define THA_ROUTE_SOFTMAX_GROUPS 1  /* softmax over all experts; choice by score + correction inside the best groups of
@@ -137,6 +142,24 @@ typedef struct {
   int fp32_scores;         /* 1: softmax weights are never rounded to bf16.  The tensor-core forms then multiply them with the
                               values as a bf16 pair hi + lo (16 mantissa bits) and sum the fp32 weights themselves; scores
                               accumulate in fp32 in every form */
+  int v_share;             /* n > 1: key head g reads value head g / n (n key heads share one value head; kv_heads % n == 0; the
+                              cache holds kv_heads / n value heads) */
+  int out_f32;             /* 1: the result is written as fp32 in every number format */
+  float q_temp_coef;       /* q_temp_every > 0: the query at position p is multiplied by */
+  int q_temp_every;        /*   1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1) */
+  int kv_shared;           /* 1: the layer writes no cache rows; cache_layer names the layer whose rows it reads (that layer runs
+                              earlier in the step).  o_k / o_v are unused */
+  /* Differential attention (diff 1): `heads` counts MAPS, two per output head, ordered per key/value group as [first maps of
+   * the group's heads | second maps]; key head 2g is the first map's, 2g + 1 the second's, both read value head g (v_share 2).
+   * tha_hyb_diff_combine makes o = a1 - diff_lambda a2, divides it by its root mean square over vdim, multiplies by diff_mult
+   * and by the head's gate. */
+  int diff;
+  float diff_lambda, diff_mult;
+  /* A short causal convolution (conv_taps > 0, no activation) over the projected q | k | v channels (q only with kv_shared)
+   * before rotation; its taps [channels, conv_taps] in projection order; the last conv_taps - 1 projected rows are state. */
+  int conv_taps;
+  const float* conv_w;
+  long long conv_state_off;
 } tha_attn_t;
 
 /* Generalized delta rule with a decay and a removal rate per key channel.  r, k, v, g: heads x dim columns each.
@@ -202,6 +225,30 @@ typedef struct {
   long long state_off;
 } tha_gla_t;
 
+/* Gated linear recurrence with a bounded forget gate.  q = silu(W_q h) (heads x dim), v = W_v h (heads x vdim),
+ * f = lower + (1 - lower) * sigmoid(W_f h + f_b) per head and key channel;  S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T,
+ * o_t = S_t^T q_t.  The read-out is divided by its root mean square per head and weighted (norm, [vdim], shared by the
+ * heads).  State per head as for tha_gla_t. */
+typedef struct {
+  int heads, dim, vdim;
+  float eps;
+  int o_q, o_f, o_v;    /* columns of the stacked input projection */
+  const float* f_b;     /* [heads * dim] */
+  const float* lower;   /* [heads * dim] */
+  const float* norm;    /* [vdim] */
+  const void* w_o;      /* [width, heads * vdim] */
+  long long state_off;
+} tha_hgrn_t;
+
+/* Residual streams.  A model keeps n copies X[0..n-1] of its residual (all equal to the embedding output at the start).
+ * A sublayer reads u = sum_s in[s] X[s], computes y = sublayer(norm(u)), and writes X'[t] = sum_s mix[s * n + t] X[s] + out[t] y
+ * for every t at once.  "The residual stream" (taps, the final norm's input) is sum_s X[s]. */
+typedef struct {
+  const float* in;      /* [n] */
+  const float* out;     /* [n] */
+  const float* mix;     /* [n, n], indexed [from, to] */
+} tha_streams_t;
+
 /* Latent attention.  Queries: c_q = rmsnorm(W_dq h) * q_norm, q = W_uq c_q, per head [dim plain | rot_dim rotated].
  * Keys and values: W_dkv h = [kv_rank | rot_dim]; c = rmsnorm(first part) * kv_norm is the cached latent, the second part
  * (rotated) is one key part shared by all heads; per head k = W_uk c, v = W_uv c.  Only [c | rotated part] is cached
@@ -236,6 +283,10 @@ typedef struct {
   int o_gate, o_up;     /* columns of the feed-forward's stacked input projection (ungated activations: o_up only) */
   const void* w_down;   /* [width, ff] */
   float act_p, act_q;   /* THA_ACT_XIELU: the two stored numbers (softplus is taken by the kernel) */
+  /* zero-initialised, the fields below keep the behaviour described above */
+  const float* b_up;    /* [ff] added to W_up h before the activation, NULL: none */
+  const float* b_down;  /* [width] added to the result, NULL: none */
+  float act_c[4];       /* THA_ACT_POLYNORM: c0..c3 */
 } tha_dense_ff_t;
 
 /* Per-token side input of a layer, after its feed-forward: e = table[token, col0 : col0 + dim];
@@ -300,6 +351,14 @@ typedef struct {
   /* before this run's first norm: x += the embedding output (pre_add_embed), then x += pre_vec ([width], NULL: none) */
   int pre_add_embed;
   const float* pre_vec;
+  tha_hgrn_t hgrn;      /* THA_MIX_HGRN */
+  /* THA_BLOCK_STREAMS: the two sublayers' stream weights; the feed-forward (dense or mixture, or none) reads norm2 through
+   * w_in2.  in_conv_taps > 0: the mixer's normed input h is replaced by h + causal_conv(h) per channel (in_conv_w
+   * [width, taps]); the last taps - 1 rows of h are state at in_conv_state_off. */
+  tha_streams_t streams1, streams2;
+  int in_conv_taps;
+  const float* in_conv_w;
+  long long in_conv_state_off;
 } tha_hyb_layer_t;
 
 typedef struct {
@@ -320,6 +379,7 @@ typedef struct {
   float embed_scale;             /* the embedding rows are multiplied by it; 0 reads as 1 */
   const void* side_table;        /* [vocab, side_cols]: the per-token side inputs of all layers, NULL: none */
   int side_cols;
+  int n_streams;                 /* THA_BLOCK_STREAMS layers: copies of the residual (0 reads as 1; at most 16) */
 } tha_hyb_model_t;
 
 /* One scheduler step: every row through every layer; logits [n_want, vocab] (fp32) of the rows listed in want_rows.
@@ -427,6 +487,34 @@ int tha_hyb_glu_clamped(void* stream, int dtype, void* y, const float* gu, long 
  * (limit, alpha)) */
 int tha_hyb_ff_act(void* stream, int dtype, int act, void* y, const float* gu, long long ldg, int col_g, int col_u, int n,
                    int ff, float limit, float alpha);
+
+/* causal convolution over `channels` adjacent columns of proj starting at col0, continuing from the slot's tail (the last
+ * taps - 1 inputs of every channel): out[r, c] = act(sum_j w[c, j] in(r - taps + 1 + j, c)) (+ in(r, c) with add_input);
+ * act 0: none, 1: silu.  out fp32 [n_rows, channels] (out_f32) or dtype-typed.  The tails are NOT advanced (tha_hyb_conv_tail). */
+int tha_hyb_conv(void* stream, int dtype, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off, const float* proj,
+                 long long ldp, int col0, int channels, int taps, const float* w, int act, int add_input, int out_f32, void* out);
+/* the tails of a convolution advanced by the step's rows */
+int tha_hyb_conv_tail(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off, const float* proj,
+                      long long ldp, int col0, int channels, int taps);
+/* Residual streams, one pass over the rows.  X [n_rows, n, width] fp32.  init (nullable): every stream is first set to
+ * init [n_rows, width].  write (nullable): X'[t] = sum_s write->mix[s, t] X[s] + write->out[t] * y, where
+ * y = dense (nullable) + bias (nullable) + sum_j weight[r, j] * down[inv[r, j]] (top picks of a mixture; top 0: none).
+ * tap, sum_out (nullable, [n_rows, width]): sum_s X[s].  read (nullable): out (fp32 with out_f32, else dtype-typed) =
+ * the norm of sum_s read->in[s] X[s]. */
+int tha_hyb_streams(void* stream, int dtype, float* X, int n, const float* init, const tha_streams_t* write, const float* dense,
+                    const float* bias, int top, const float* weight, const int* inv, const float* down, float* tap, float* sum_out,
+                    const tha_streams_t* read, const tha_norm_t* norm, float eps, int out_f32, void* out, int n_rows, int width);
+/* y (dtype-typed [n, ff]) = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 of z = gu[r, col_u ..] + bias (nullable) */
+int tha_hyb_polynorm(void* stream, int dtype, void* y, const float* gu, long long ldg, int col_u, const float* bias, const float* c,
+                     float eps, int n, int ff);
+/* differential attention's combination (tha_attn_t::diff): att fp32 [n_rows, a->heads * vdim] in map order -> out dtype-typed
+ * [n_rows, a->heads / 2 * vdim] in head order; gate columns at a->o_g of proj when a->head_gate */
+int tha_hyb_diff_combine(void* stream, int dtype, const tha_attn_t* a, const float* att, const float* proj, long long ldp, void* out,
+                         int n_rows);
+/* the bounded-forget-gate recurrence over the rows of every sequence in order: the q columns of proj are replaced by their silu,
+ * the f columns by 1 - f, decay [n_rows, heads * dim] receives f; read-out to o_raw (fp32), normed to out (dtype-typed) */
+int tha_hyb_hgrn_scan(void* stream, int dtype, const tha_hgrn_t* g, const tha_rows_t* rows, const tha_state_store_t* st, float* proj,
+                      long long ldp, float* decay, float* o_raw, void* out);
 
 #ifdef __cplusplus
 }
