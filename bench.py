@@ -56,7 +56,7 @@ def parse_args():
                     "over the GPUs, all-reduce fused into its consumer over NVLink peer memory (strong scaling)")
     ap.add_argument("--pos0", type=int, default=0, help="profiling aid: slots start at this position over a zero-filled KV cache "
                     "(same bytes and time per step as a real context of that length); the default 0 is the benchmark")
-    ap.add_argument("--design", default="", choices=["", "timerax", "numizen", "bozovik"], help="instead of the default workload: prompt and decode throughput of "
+    ap.add_argument("--design", default="", choices=["", "timerax", "numizen", "bozovik", "mozetar"], help="instead of the default workload: prompt and decode throughput of "
                     "this layer-program design at a few realistic layer sizes (random weights), beside the llama2 bf16 path at equal size")
     ap.add_argument("--design-sizes", default="w1024,w2048")
     ap.add_argument("--design-prompt", type=int, default=4096)

@@ -2,7 +2,8 @@
 Numizen beside Timerax -- the closest design the framework has: attention + a recurrent mixer + a mixture of experts --
 and llama2 at equal size (bench.py --design numizen); or of Bozovik beside Numizen with dense feed-forwards -- the closest
 design the framework has: latent attention + a recurrent mixer + a looped segment -- and llama2 at equal size (bench.py
---design bozovik).
+--design bozovik); or of Mozetar beside Numizen -- the closest design the framework has: softmax attention + a gated linear
+recurrence + a mixture of experts behind a softmax router with groups -- and llama2 at equal size (bench.py --design mozetar).
 
 Random weights at sizes that resemble a real model's layers; a few layers only, so that building the folder stays
 short.  For every size: prompt ingestion (one prompt in one step) and batched decoding (one token per live request per
@@ -90,6 +91,32 @@ def bozovik_config(s: dict, n: dict) -> dict:
     layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": mlp} for i in range(s["layers"])]
     return {"architecture": "Bozovik", "layers": layers, "norm": {"eps": 1e-5}, "vocab": s["vocab"], "width": s["width"], "residual_mult": 0.7,
             "embedding": {"scale": 1.0}, "token_side": {"dim": n["side"]}, "loop": {"start": 1, "stop": min(3, s["layers"]), "times": 1}}
+
+
+# Mozetar at the same widths, expert sizes and vocabulary: windowed attention with short convolutions (heads of 128, rotary on
+# half of a head), the gated linear recurrence with Numizen's linear-attention head sizes, differential attention (two maps of
+# 64 channels per head, values of 128), and a windowed layer that reads layer 0's cache rows; three residual streams; a dense
+# PolyNorm feed-forward as wide as the experts a token uses in layer 0, the mixture (silu experts, router groups) elsewhere.
+MOZETAR = {
+    "w1024": dict(window=1024, gheads=4, gdim=128, gvdim=256, ddim=64, groups=(4, 2)),
+    "w2048": dict(window=2048, gheads=8, gdim=128, gvdim=256, ddim=64, groups=(4, 2)),
+}
+
+
+def mozetar_config(s: dict, n: dict) -> dict:
+    rot = {"base": 500000.0, "dims": s["dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}
+    win = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "conv": 4, "scale": s["dim"] ** -0.5,
+           "mask": {"size": n["window"]}, "rot": rot}
+    dif = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": n["ddim"], "vdim": s["dim"], "scale": n["ddim"] ** -0.5, "diff": 0.6,
+           "q_temp": {"coef": 0.1, "every": 512}}
+    rec = {"heads": n["gheads"], "dim": n["gdim"], "vdim": n["gvdim"]}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"]},
+           "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": n["groups"][0], "keep": n["groups"][1]}}}
+    dense = {"kind": "dense", "ff": s["top"] * s["ff"] + s["sff"]}
+    kinds = [("attention_2", win), ("attention", dif), ("hgrn2", rec), ("attention_2", dict(win, kv_from=0))]
+    layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": dense if i == 0 else moe} for i in range(s["layers"])]
+    return {"architecture": "Mozetar", "layers": layers, "norm": {"eps": 1e-6}, "canon": {"taps": 3}, "streams": 3, "vocab": s["vocab"],
+            "width": s["width"]}
 
 
 def _time_timerax(serving, folder, prompt_len, batch, ctx, steps, warmup, kernels):
@@ -223,6 +250,28 @@ def run(load_pkg, sizes, prompt_len=4096, batch=64, ctx=512, steps=16, warmup=3,
     for name in sizes:
         s = SIZES[name]
         r = {}
+        if design == "mozetar":
+            mcfg = mozetar_config(s, MOZETAR[name])
+            tmp = tempfile.mkdtemp(prefix="design_bench_")
+            try:
+                serving.save_model_folder(tmp, mcfg, serving.random_mozetar_tensors(mcfg, 0))
+                r["mozetar"] = _time_folder(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)
+                r["mozetar"]["weights_bytes"] = timerax_weight_bytes(mcfg, serving.mozetar_tensor_shapes(mcfg))
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            if not kernels:
+                ncfg = numizen_config(s, NUMIZEN[name], max_positions=max(prompt_len, ctx + steps + warmup) + 64)
+                tmp = tempfile.mkdtemp(prefix="design_bench_")
+                try:
+                    serving.save_model_folder(tmp, ncfg, serving.random_numizen_tensors(ncfg, 0))
+                    r["numizen"] = _time_folder(serving, tmp, prompt_len, batch, ctx, steps, warmup, kernels)
+                    r["numizen"]["weights_bytes"] = timerax_weight_bytes(ncfg, serving.numizen_tensor_shapes(ncfg))
+                finally:
+                    shutil.rmtree(tmp, ignore_errors=True)
+                if llama:
+                    r["llama2_bf16_equal_size"] = _time_llama(engine_mod, checkpoint_mod, s, prompt_len, batch, ctx, steps, warmup)
+            results[name] = r
+            continue
         if design == "bozovik":
             bcfg = bozovik_config(s, BOZOVIK[name])
             tmp = tempfile.mkdtemp(prefix="design_bench_")

@@ -49,8 +49,10 @@ static void mozetar_mixer(const JsonValue& L, const std::string& pre, int index,
     ls.mixer = THA_MIX_ATTN;
     AttnSpec& a = ls.attn;
     mozetar_attention_sizes(m, p, &a);
-    a.conv_taps = m.at("conv").integer();
-    if (a.conv_taps < 1) throw std::runtime_error("config: 'conv' must be at least one tap");
+    if (m.has("conv")) {   // absent: the projections are used as they are
+      a.conv_taps = m.at("conv").integer();
+      if (a.conv_taps < 1) throw std::runtime_error("config: 'conv' must be at least one tap");
+    }
     if (m.has("rot")) {
       const JsonValue& r = m.at("rot");
       a.rotary = true;
@@ -65,9 +67,11 @@ static void mozetar_mixer(const JsonValue& L, const std::string& pre, int index,
         a.rot.original = sc.at("original").number();
       }
     }
-    a.window = m.at("mask").at("size").integer();
-    if (a.window < 1) throw std::runtime_error("config: a window must hold at least the token itself");
-    if (m.has("kv_from") && m.at("kv_from").kind != JsonValue::Null) {
+    if (m.has("mask")) {   // absent: every earlier position is seen
+      a.window = m.at("mask").at("size").integer();
+      if (a.window < 1) throw std::runtime_error("config: a window must hold at least the token itself");
+    }
+    if (m.has("kv_from")) {
       a.kv_from = m.at("kv_from").integer();
       if (a.kv_from < 0 || a.kv_from >= index) throw std::runtime_error("config: 'kv_from' must name an earlier layer");
     }
@@ -110,7 +114,7 @@ static void mozetar_translate(const JsonValue& c, LayerProgramSpec* out) {
     ls.streams1 = {pre + "hc1.in", pre + "hc1.out", pre + "hc1.mix"};
     if (canon_taps > 0) { ls.in_conv = pre + "canon1"; ls.in_conv_taps = canon_taps; }
     mozetar_mixer(L, pre, i, n, &ls);
-    if (L.has("mlp") && L.at("mlp").kind != JsonValue::Null) {
+    if (L.has("mlp")) {   // absent or null: the layer has no feed-forward
       const JsonValue& f = L.at("mlp");
       const std::string kind = f.at("kind").string();
       const std::string q = pre + "mlp.";
@@ -132,7 +136,7 @@ static void mozetar_translate(const JsonValue& c, LayerProgramSpec* out) {
         e.ff = f.at("expert").at("ff").integer();
         e.act = THA_ACT_SILU_GLU;
         e.route = THA_ROUTE_SOFTMAX_GROUPS;
-        if (r.has("groups") && r.at("groups").kind != JsonValue::Null) {
+        if (r.has("groups")) {
           e.groups = r.at("groups").at("count").integer();
           e.keep_groups = r.at("groups").at("keep").integer();
         }

@@ -381,3 +381,79 @@ def random_bozovik_tensors(cfg: dict, seed: int = 0, decay_rank: int = 16) -> di
             a = 1.0 + 0.2 * rng.standard_normal(shape)
         out[name] = np.asarray(a, dtype=np.float32)
     return out
+
+
+def mozetar_tensor_shapes(cfg: dict) -> dict:
+    """name -> shape of every tensor a Mozetar config asks for."""
+    W, V, n = cfg["width"], cfg["vocab"], cfg.get("streams", 1)
+    s = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+    for i, L in enumerate(cfg["layers"]):
+        p, m, q = f"l{i}.", L["mixer"], f"l{i}.mix."
+        s[p + "norm1"] = (W,)
+        if "canon" in cfg:
+            s[p + "canon1"] = (W, cfg["canon"]["taps"])
+        for k in (1, 2) if L.get("mlp") else (1,):
+            s[p + f"hc{k}.in"], s[p + f"hc{k}.out"], s[p + f"hc{k}.mix"] = (n,), (n,), (n, n)
+        if L["type"] == "attention":
+            H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            s[q + "q"], s[q + "k"], s[q + "v"], s[q + "g"], s[q + "o"] = (2 * H * D, W), (2 * G * D, W), (G * E, W), (H, W), (W, H * E)
+            for v in ("lq1", "lk1", "lq2", "lk2"):
+                s[q + v] = (D,)
+        elif L["type"] == "attention_2":
+            H, G, D, E, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m.get("conv", 0)
+            s[q + "q"], s[q + "o"] = (H * D, W), (W, H * E)
+            if taps:
+                s[q + "q.conv"] = (H * D, taps)
+            if m.get("kv_from") is None:
+                s[q + "k"], s[q + "v"] = (G * D, W), (G * E, W)
+                if taps:
+                    s[q + "k.conv"], s[q + "v.conv"] = (G * D, taps), (G * E, taps)
+        elif L["type"] == "hgrn2":
+            H, D, E = m["heads"], m["dim"], m["vdim"]
+            s[q + "q"], s[q + "f"], s[q + "v"], s[q + "o"] = (H * D, W), (H * D, W), (H * E, W), (W, H * E)
+            s[q + "f.b"], s[q + "lower"], s[q + "norm"] = (H * D,), (H * D,), (E,)
+        else:
+            raise ValueError(L["type"])
+        f = L.get("mlp")
+        if f:
+            s[p + "norm2"] = (W,)
+            q = p + "mlp."
+            if f["kind"] == "dense":
+                s[q + "up"], s[q + "up.b"], s[q + "down"], s[q + "down.b"], s[q + "act"] = (f["ff"], W), (f["ff"],), (W, f["ff"]), (W,), (4,)
+            else:
+                s[q + "router"] = (f["router"]["experts"], W)
+                for e in range(f["router"]["experts"]):
+                    s[q + f"e{e}.gate"], s[q + f"e{e}.up"], s[q + f"e{e}.down"] = (f["expert"]["ff"], W), (f["expert"]["ff"], W), (W, f["expert"]["ff"])
+    return s
+
+
+def random_mozetar_tensors(cfg: dict, seed: int = 0) -> dict:
+    """Random weights of a Mozetar config: matrices N(0, 1/in), norm weights around one, stream weights near an even read and an
+    identity mixing, forget-gate bounds spread over (0, 0.9), convolution taps of order one half."""
+    rng = np.random.default_rng(seed)
+    n = cfg.get("streams", 1)
+    out = {}
+    for name, shape in mozetar_tensor_shapes(cfg).items():
+        last = name.rsplit(".", 1)[-1]
+        if last in ("conv", "canon1"):
+            a = 0.5 * rng.standard_normal(shape)
+        elif last == "in":
+            a = 1.0 / n + 0.1 * rng.standard_normal(shape)
+        elif last == "out":
+            a = 1.0 + 0.1 * rng.standard_normal(shape)
+        elif last == "mix":
+            a = np.eye(n) + 0.1 * rng.standard_normal(shape)
+        elif last == "lower":
+            a = rng.uniform(0.0, 0.9, shape)
+        elif last in ("lq1", "lk1", "lq2", "lk2"):
+            a = 0.3 * rng.standard_normal(shape)
+        elif last == "act":
+            a = np.array([0.6, 0.3, 0.2, 0.05])
+        elif last == "b":
+            a = 0.1 * rng.standard_normal(shape)
+        elif len(shape) == 2:
+            a = rng.standard_normal(shape, dtype=np.float32) * (1.0 if name == "embed" else 1.0 / np.sqrt(shape[1]))
+        else:
+            a = 1.0 + 0.2 * rng.standard_normal(shape)
+        out[name] = np.asarray(a, dtype=np.float32)
+    return out

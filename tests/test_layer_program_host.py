@@ -9,6 +9,7 @@ import numpy as np
 import pytest
 
 import bozovik_oracle as B
+import mozetar_oracle as M
 import numizen_oracle as N
 import timerax_oracle as O
 from pkgload import load_pkg
@@ -42,7 +43,7 @@ def test_registry_names_what_it_knows(tmp_path):
     with pytest.raises(serving.ServingError) as e:
         serving.ServingEngine(str(tmp_path), "float32", 64, 1)
     assert "Nope" in str(e.value) and "Timerax" in str(e.value) and "llama2" in str(e.value) and "Numizen" in str(e.value)
-    assert "Bozovik" in str(e.value)
+    assert "Bozovik" in str(e.value) and "Mozetar" in str(e.value)
 
 
 @built
@@ -272,3 +273,82 @@ def test_plain_delta_rule_removes_along_the_unit_key():
     B.delta_mixer(h, {"heads": 1, "dim": D}, W, "p.", 1e-6, st)
     # after token 1: S = k v^T (4 at [0, 0]); token 2 removes u u^T S = all of it and writes k v^T again
     assert np.allclose(st["S"][0], np.diag([4.0, 0, 0, 0]), atol=1e-5)
+
+
+# ---- Mozetar ----------------------------------------------------------------------------------------------------------
+def _mozetar_cfg(layers, **extra):
+    c = {"architecture": "Mozetar", "width": 16, "vocab": 20, "norm": {"eps": 1e-5}, "streams": 2, "canon": {"taps": 2}, "layers": layers}
+    c.update(extra)
+    return c
+
+
+@built
+def test_mozetar_configs_are_refused_by_name(tmp_path):
+    serving = load_pkg("serving")
+    win = {"type": "attention_2", "mixer": {"heads": 2, "kv_heads": 1, "dim": 4, "vdim": 4, "scale": 0.5, "conv": 2, "mask": {"size": 3}}, "mlp": None}
+    dif = {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 4, "vdim": 4, "scale": 0.5}, "mlp": None}
+    for cfg, word in [(_mozetar_cfg([{"type": "helix", "mixer": {}, "mlp": None}]), "helix"),
+                      (_mozetar_cfg([dict(win, mlp={"kind": "sparse"})]), "sparse"),
+                      (_mozetar_cfg([dif]), "diff"),
+                      (_mozetar_cfg([dict(win, mixer=dict(win["mixer"], mask={"size": 0}))]), "window"),
+                      (_mozetar_cfg([dict(win, mixer=dict(win["mixer"], kv_from=0))]), "kv_from"),
+                      (_mozetar_cfg([win], streams=40), "streams"),
+                      (_mozetar_cfg([win], canon={"taps": 0}), "canon"),
+                      ({k: v for k, v in _mozetar_cfg([win]).items() if k != "vocab"}, "vocab")]:
+        (tmp_path / "config.json").write_text(json.dumps(cfg))
+        with pytest.raises(serving.ServingError) as e:
+            serving.ServingEngine(str(tmp_path), "float32", 64, 1)
+        assert word in str(e.value), (word, str(e.value))
+
+
+def test_mozetar_tensor_shapes_cover_a_config():
+    serving = load_pkg("serving")
+    win = {"heads": 4, "kv_heads": 2, "dim": 6, "vdim": 5, "scale": 0.4, "conv": 3, "mask": {"size": 7}, "rot": {"base": 100.0, "dims": 4}}
+    layers = [{"type": "attention_2", "mixer": win, "mlp": {"kind": "dense", "ff": 12}},
+              {"type": "hgrn2", "mixer": {"heads": 2, "dim": 3, "vdim": 7}, "mlp": None},
+              {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 3, "vdim": 5, "scale": 0.5, "diff": 0.2},
+               "mlp": {"kind": "moe", "expert": {"ff": 6}, "router": {"experts": 4, "top": 2}}},
+              {"type": "attention_2", "mixer": dict(win, kv_from=0), "mlp": None}]
+    cfg = _mozetar_cfg(layers, streams=3)
+    t = serving.random_mozetar_tensors(cfg, 0)
+    assert t["l0.mix.q"].shape == (24, 16) and t["l0.mix.k.conv"].shape == (12, 3) and t["l0.mix.v.conv"].shape == (10, 3)
+    assert t["l0.canon1"].shape == (16, 2) and t["l0.hc2.mix"].shape == (3, 3) and t["l0.mlp.act"].shape == (4,) and t["l0.mlp.up.b"].shape == (12,)
+    assert t["l1.mix.lower"].shape == (6,) and t["l1.mix.norm"].shape == (7,) and "l1.hc2.in" not in t and "l1.norm2" not in t
+    assert t["l2.mix.q"].shape == (24, 16) and t["l2.mix.k"].shape == (12, 16) and t["l2.mix.v"].shape == (10, 16) and t["l2.mix.g"].shape == (4, 16)
+    assert t["l2.mlp.e3.down"].shape == (16, 6) and t["l2.mlp.router"].shape == (4, 16)
+    assert "l3.mix.k" not in t and "l3.mix.v.conv" not in t and t["l3.mix.q.conv"].shape == (24, 3)
+    assert set(t) == set(M.tensor_shapes(cfg))
+
+
+def test_plain_mozetar_statements_agree():
+    assert M.self_check()
+
+
+def test_plain_mozetar_convolution_recurrence_and_router():
+    # the convolution's last tap multiplies the current input, the first tap the oldest; zeros before the start, then the tail
+    w = np.array([[1.0, 10.0, 100.0]])
+    y, tail = M.causal_conv(np.array([[1.0], [2.0], [3.0]]), w, np.zeros((2, 1)))
+    assert y[:, 0].tolist() == [100.0, 210.0, 321.0] and tail[:, 0].tolist() == [2.0, 3.0]
+    y2, _ = M.causal_conv(np.array([[4.0]]), w, tail)
+    assert y2[0, 0] == 432.0
+    # a closed gate (f = 1) keeps the state and writes nothing; an open gate at bound `lower` keeps that share
+    D, E = 2, 2
+    W = {"p.q": np.eye(D), "p.f": np.zeros((D, D)), "p.f.b": np.array([40.0, -40.0]), "p.lower": np.array([0.0, 0.25]), "p.v": np.eye(E),
+         "p.norm": np.ones(E), "p.o": np.eye(E)}
+    st = {"S": np.ones((1, D, E))}
+    M.hgrn2_mixer(np.array([[3.0, 5.0]]), {"heads": 1, "dim": D, "vdim": E}, W, "p.", 1e-6, st)
+    assert np.allclose(st["S"][0, 0], [1.0, 1.0])                        # f = 1: kept
+    assert np.allclose(st["S"][0, 1], [0.25 + 0.75 * 3.0, 0.25 + 0.75 * 5.0])   # f = lower: a quarter kept, three quarters of v written
+    # router: the best group only; weights are the chosen scores over their sum
+    r = {"experts": 4, "top": 2, "groups": {"count": 2, "keep": 1}}
+    ids, wts = M.route(np.array([[1.0]]), r, {"p.router": np.array([[0.0], [3.0], [2.0], [2.5]])}, "p.")
+    assert ids[0].tolist() == [1, 0] and np.isclose(wts[0].sum(), 1.0) and wts[0, 0] > wts[0, 1]
+    ids, _ = M.route(np.array([[1.0]]), {"experts": 4, "top": 2}, {"p.router": np.array([[0.0], [3.0], [2.0], [2.5]])}, "p.")
+    assert ids[0].tolist() == [1, 3]
+    # rotation pairs neighbours: entries (0, 1) turn together, entries from `dims` on pass
+    x = np.arange(6, dtype=np.float64).reshape(1, 1, 6)
+    y = M.rotate_pairs(x, [1], {"dims": 2, "base": 1.0})
+    assert np.allclose(y[0, 0, 2:], [2, 3, 4, 5]) and np.isclose(y[0, 0, 0], 0.0 * np.cos(1.0) - 1.0 * np.sin(1.0))
+    # PolyNorm: each power is normed by itself, so scaling the input leaves everything but the constant's share unchanged
+    z = np.array([[1.0, -2.0, 3.0]])
+    assert np.allclose(M.polynorm(z, [0.5, 0.3, 0.2, 0.1], 0.0), M.polynorm(7.0 * z, [0.5, 0.3, 0.2, 0.1], 0.0))
