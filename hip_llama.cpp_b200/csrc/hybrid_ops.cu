@@ -1143,10 +1143,63 @@ __global__ void hyb_head_gate_kernel(T* __restrict__ out, const float* __restric
 // ------------------------------------------------------------------------------------------------------------------
 // short causal convolution + silu; the slot keeps the last taps-1 inputs of every channel (oldest first)
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T>
+// V channels per thread (V = 4: 128-bit reads of the rows; the caller checks the alignment); taps up to CONV_MAX_TAPS keep their
+// weights in registers across the rows a thread walks
+constexpr int CONV_MAX_TAPS = 8;
+template <typename T, int V>
 __global__ void hyb_conv_kernel(tha_rows_t rows, tha_state_store_t st, long long conv_state_off, const float* __restrict__ proj,
                                 long long ldp, int col0, int channels, int taps, const float* __restrict__ w, int act, int add_input,
                                 T* __restrict__ out) {
+  const int c = V * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (c >= channels) return;
+  float wr[CONV_MAX_TAPS][V];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; j++)
+#pragma unroll
+    for (int v = 0; v < V; v++) wr[j][v] = j < taps ? w[(size_t)(c + v) * taps + j] : 0.f;
+  for (int r = blockIdx.y; r < rows.n_rows; r += gridDim.y) {
+    const int s = rows.row_seq[r], first = rows.seq_first[s];
+    const float* tail = st.base + (size_t)rows.seq_slot[s] * st.slot_floats + conv_state_off + (size_t)c * (taps - 1);
+    float acc[V], x[V], cur[V];
+#pragma unroll
+    for (int v = 0; v < V; v++) acc[v] = 0.f;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; j++) {
+      if (j >= taps) break;
+      const int rr = r - (taps - 1 - j);
+      if (rr >= first) {
+        if (V == 4) { const float4 t = *reinterpret_cast<const float4*>(proj + (size_t)rr * ldp + col0 + c); x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w; }
+        else x[0] = proj[(size_t)rr * ldp + col0 + c];
+      } else {
+#pragma unroll
+        for (int v = 0; v < V; v++) x[v] = tail[(size_t)v * (taps - 1) + (taps - 1) - (first - rr)];
+      }
+#pragma unroll
+      for (int v = 0; v < V; v++) { acc[v] = fmaf(wr[j][v], x[v], acc[v]); cur[v] = x[v]; }
+    }
+#pragma unroll
+    for (int v = 0; v < V; v++) {
+      if (act == 1) acc[v] = acc[v] / (1.0f + expf(-acc[v]));
+      if (add_input) acc[v] += cur[v];                       // the last tap's input is the row itself
+    }
+    T* dst = out + (size_t)r * channels + c;
+    if (V == 4 && sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else if (V == 4) {
+      uint2 pk;
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
+      pk.x = *reinterpret_cast<const unsigned*>(&lo); pk.y = *reinterpret_cast<const unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = pk;
+    } else {
+      hyb_store(dst, acc[0]);
+    }
+  }
+}
+// any number of taps, a channel per thread
+template <typename T>
+__global__ void hyb_conv_long_kernel(tha_rows_t rows, tha_state_store_t st, long long conv_state_off, const float* __restrict__ proj,
+                                     long long ldp, int col0, int channels, int taps, const float* __restrict__ w, int act, int add_input,
+                                     T* __restrict__ out) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   for (int r = blockIdx.y; r < rows.n_rows; r += gridDim.y) {
@@ -1712,13 +1765,21 @@ extern "C" int tha_hyb_conv(void* stream, int dtype, const tha_rows_t* rows, con
   if (rows->n_rows < 1 || channels < 1) return THA_STATUS_SUCCESS;
   if (taps < 1) return THA_STATUS_INVALID_ARG;
   cudaStream_t s = (cudaStream_t)stream;
-  const dim3 grid(ceil_div(channels, 128), rows->n_rows < 65535 ? rows->n_rows : 65535);
-  if (out_f32 || dtype == THA_DT_F32)
-    THA_CUDA_OK(launch(hyb_conv_kernel<float>, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act,
-                       add_input, (float*)out));
-  else
-    THA_CUDA_OK(launch(hyb_conv_kernel<bf16>, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act,
-                       add_input, (bf16*)out));
+  const int gy = rows->n_rows < 65535 ? rows->n_rows : 65535;
+  const bool f32 = out_f32 || dtype == THA_DT_F32;
+#define CONV_GO(KF, KB, per)                                                                                                              \
+  do {                                                                                                                                    \
+    const dim3 grid(ceil_div(ceil_div(channels, per), 128), gy);                                                                         \
+    if (f32) THA_CUDA_OK(launch(KF, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act, add_input, \
+                                (float*)out));                                                                                            \
+    else THA_CUDA_OK(launch(KB, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act, add_input,     \
+                            (bf16*)out));                                                                                                 \
+  } while (0)
+  if (taps > CONV_MAX_TAPS) CONV_GO(hyb_conv_long_kernel<float>, hyb_conv_long_kernel<bf16>, 1);
+  else if (channels % 4 == 0 && ldp % 4 == 0 && col0 % 4 == 0 && aligned16(proj) && aligned16(out))
+    CONV_GO((hyb_conv_kernel<float, 4>), (hyb_conv_kernel<bf16, 4>), 4);
+  else CONV_GO((hyb_conv_kernel<float, 1>), (hyb_conv_kernel<bf16, 1>), 1);
+#undef CONV_GO
   return THA_STATUS_SUCCESS;
 }
 extern "C" int tha_hyb_conv_tail(void* stream, const tha_rows_t* rows, const tha_state_store_t* st, long long conv_state_off,

@@ -29,9 +29,29 @@ struct StreamsArgs {
   int width;
 };
 
-template <int NS, typename T>
-__global__ void __launch_bounds__(256) hyb_streams_kernel(StreamsArgs a, T* __restrict__ out) {
-  extern __shared__ float u_row[];   // [width] when a read follows
+// V consecutive floats (V = 4: one 128-bit access; the callers check the alignment)
+template <int V> __device__ __forceinline__ void ldv(const float* p, float* o) {
+  if (V == 4) { const float4 t = *reinterpret_cast<const float4*>(p); o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w; }
+  else o[0] = *p;
+}
+template <int V> __device__ __forceinline__ void stv(float* p, const float* o) {
+  if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  else *p = o[0];
+}
+template <int V> __device__ __forceinline__ void stv(__nv_bfloat16* p, const float* o) {
+  if (V == 4) {
+    uint2 pk;
+    const __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2], o[3]);
+    pk.x = *reinterpret_cast<const unsigned*>(&a); pk.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = pk;
+  } else {
+    *p = __float2bfloat16_rn(o[0]);
+  }
+}
+
+template <int NS, typename T, int V>
+__global__ void __launch_bounds__(512) hyb_streams_kernel(StreamsArgs a, T* __restrict__ out) {
+  extern __shared__ __align__(16) float u_row[];   // [width] when a read follows
   __shared__ float red[33];
   __shared__ float c_mix[NS * NS], c_out[NS], c_in[NS];
   const int r = blockIdx.x, n = a.n, W = a.width;
@@ -46,43 +66,72 @@ __global__ void __launch_bounds__(256) hyb_streams_kernel(StreamsArgs a, T* __re
   __syncthreads();
   float* xr = a.X + (size_t)r * n * W;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float x[NS];
+  for (int i = V * threadIdx.x; i < W; i += V * blockDim.x) {
+    float x[NS][V];
 #pragma unroll
-    for (int s = 0; s < NS; s++) x[s] = s < n ? (a.init ? a.init[(size_t)r * W + i] : xr[(size_t)s * W + i]) : 0.f;
+    for (int s = 0; s < NS; s++) {
+      if (s < n) ldv<V>(a.init ? a.init + (size_t)r * W + i : xr + (size_t)s * W + i, x[s]);
+      else
+#pragma unroll
+        for (int v = 0; v < V; v++) x[s][v] = 0.f;
+    }
     if (a.w_out) {
-      float y = a.dense ? a.dense[(size_t)r * W + i] : 0.f;
-      if (a.bias) y += a.bias[i];
-      for (int j = 0; j < a.top; j++) y = fmaf(a.weight[(size_t)r * a.top + j], a.down[(size_t)a.inv[(size_t)r * a.top + j] * W + i], y);
-      float nx[NS];
+      float y[V], t4[V];
 #pragma unroll
-      for (int t = 0; t < NS; t++) {
-        float v = c_out[t] * y;
+      for (int v = 0; v < V; v++) y[v] = 0.f;
+      if (a.dense) ldv<V>(a.dense + (size_t)r * W + i, y);
+      if (a.bias) {
+        ldv<V>(a.bias + i, t4);
 #pragma unroll
-        for (int s = 0; s < NS; s++) v = fmaf(c_mix[s * NS + t], x[s], v);
-        nx[t] = v;
+        for (int v = 0; v < V; v++) y[v] += t4[v];
       }
+      for (int j = 0; j < a.top; j++) {
+        const float wj = a.weight[(size_t)r * a.top + j];
+        ldv<V>(a.down + (size_t)a.inv[(size_t)r * a.top + j] * W + i, t4);
 #pragma unroll
-      for (int t = 0; t < NS; t++) x[t] = nx[t];
+        for (int v = 0; v < V; v++) y[v] = fmaf(wj, t4[v], y[v]);
+      }
+      float nx[NS][V];
+#pragma unroll
+      for (int t = 0; t < NS; t++)
+#pragma unroll
+        for (int v = 0; v < V; v++) {
+          float acc = c_out[t] * y[v];
+#pragma unroll
+          for (int s = 0; s < NS; s++) acc = fmaf(c_mix[s * NS + t], x[s][v], acc);
+          nx[t][v] = acc;
+        }
+#pragma unroll
+      for (int t = 0; t < NS; t++)
+#pragma unroll
+        for (int v = 0; v < V; v++) x[t][v] = nx[t][v];
     }
     if (a.w_out || a.init) {
 #pragma unroll
       for (int s = 0; s < NS; s++)
-        if (s < n) xr[(size_t)s * W + i] = x[s];
+        if (s < n) stv<V>(xr + (size_t)s * W + i, x[s]);
     }
     if (a.tap || a.sum_out) {
-      float sum = 0.f;
+      float sum[V];
 #pragma unroll
-      for (int s = 0; s < NS; s++) sum += x[s];
-      if (a.tap) a.tap[(size_t)r * W + i] = sum;
-      if (a.sum_out) a.sum_out[(size_t)r * W + i] = sum;
+      for (int v = 0; v < V; v++) {
+        sum[v] = 0.f;
+#pragma unroll
+        for (int s = 0; s < NS; s++) sum[v] += x[s][v];
+      }
+      if (a.tap) stv<V>(a.tap + (size_t)r * W + i, sum);
+      if (a.sum_out) stv<V>(a.sum_out + (size_t)r * W + i, sum);
     }
     if (a.r_in) {
-      float u = 0.f;
+      float u[V];
 #pragma unroll
-      for (int s = 0; s < NS; s++) u = fmaf(c_in[s], x[s], u);
-      u_row[i] = u;
-      ss = fmaf(u, u, ss);
+      for (int v = 0; v < V; v++) {
+        u[v] = 0.f;
+#pragma unroll
+        for (int s = 0; s < NS; s++) u[v] = fmaf(c_in[s], x[s][v], u[v]);
+        ss = fmaf(u[v], u[v], ss);
+      }
+      stv<V>(u_row + i, u);
     }
   }
   if (!a.r_in) return;
@@ -91,9 +140,15 @@ __global__ void __launch_bounds__(256) hyb_streams_kernel(StreamsArgs a, T* __re
     ss = block_sum(ss, red);
     inv = 1.0f / sqrtf(ss / (float)W + a.eps);
   }
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {   // a thread reads back the entries it wrote
-    const float v = a.norm_kind == THA_NORM_RMS ? u_row[i] * inv * (a.norm_off + a.norm_w[i]) : u_row[i];
-    hyb_store(out + (size_t)r * W + i, v);
+  for (int i = V * threadIdx.x; i < W; i += V * blockDim.x) {   // a thread reads back the entries it wrote
+    float u[V], w[V];
+    ldv<V>(u_row + i, u);
+    if (a.norm_kind == THA_NORM_RMS) {
+      ldv<V>(a.norm_w + i, w);
+#pragma unroll
+      for (int v = 0; v < V; v++) u[v] = u[v] * inv * (a.norm_off + w[v]);
+    }
+    stv<V>(out + (size_t)r * W + i, u);
   }
 }
 
@@ -140,14 +195,20 @@ __global__ void hyb_diff_combine_kernel(T* __restrict__ out, const float* __rest
 template <int NS>
 static int streams_launch(cudaStream_t s, const StreamsArgs& a, int out_kind, void* out, int n_rows) {
   const size_t smem = a.r_in ? (size_t)a.width * sizeof(float) : 0;
-  const int nt = a.width >= 1024 ? 256 : 128;
-#define STREAMS_GO(T)                                                                                                                  \
+  // four columns per thread where every row starts on a 16-byte boundary
+  constexpr int VV = NS <= 4 ? 4 : 1;   // more streams than four would not fit a thread's registers four columns at a time
+  const bool vec = VV == 4 && a.width % 4 == 0 && aligned16(a.X) && aligned16(a.init) && aligned16(a.dense) && aligned16(a.bias) && aligned16(a.down) &&
+                   aligned16(a.tap) && aligned16(a.sum_out) && aligned16(a.norm_w) && aligned16(out);
+  const int per = vec ? 4 : 1;
+  int nt = 64;
+  while (nt < 512 && nt * per < a.width) nt *= 2;
+#define STREAMS_GO(T, V)                                                                                                               \
   do {                                                                                                                                 \
-    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_streams_kernel<NS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    THA_CUDA_OK(launch(hyb_streams_kernel<NS, T>, dim3(n_rows), dim3(nt), smem, s, false, a, (T*)out));                                \
+    if (smem > 48 * 1024) THA_CUDA_OK(cudaFuncSetAttribute(hyb_streams_kernel<NS, T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    THA_CUDA_OK(launch(hyb_streams_kernel<NS, T, V>, dim3(n_rows), dim3(nt), smem, s, false, a, (T*)out));                             \
   } while (0)
-  if (out_kind == 0) STREAMS_GO(float);
-  else STREAMS_GO(__nv_bfloat16);
+  if (out_kind == 0) { if (vec) STREAMS_GO(float, VV); else STREAMS_GO(float, 1); }
+  else { if (vec) STREAMS_GO(__nv_bfloat16, VV); else STREAMS_GO(__nv_bfloat16, 1); }
 #undef STREAMS_GO
   return THA_STATUS_SUCCESS;
 }

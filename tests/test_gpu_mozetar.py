@@ -267,7 +267,7 @@ def test_mixture_router_groups(tmp_path, experts, top, groups):
         w["l0.mlp.router"][...] *= 4.0                           # scores far from even: the kept groups differ from token to token
     b = one_layer(tmp_path, recurrent(moe(experts=experts, top=top, ff=12, groups=groups)), tweak=tweak)
     got, z = check_all_positions(b, n=80)
-    if groups and groups[1] < groups[0]:                         # the groups do bind: without them other experts are chosen
+    if groups and groups[1] < min(top, groups[0]):               # fewer kept groups than picks: the groups do bind
         free = copy.deepcopy(b.cfg)
         del free["layers"][0]["mlp"]["router"]["groups"]
         assert rel_err(O.forward(free, b.w, tokens_for(b, 80, 9))[0], z) > 1e-2
@@ -280,7 +280,7 @@ def test_residual_streams(tmp_path, streams):
         rng = np.random.default_rng(8)
         for i in range(2):
             for q in ("hc1", "hc2"):
-                w["l%d.%s.mix" % (i, q)][...] = 0.6 * np.eye(streams) + 0.5 * rng.standard_normal((streams, streams))
+                w["l%d.%s.mix" % (i, q)][...] = 0.6 * np.eye(streams) + 0.5 * rng.standard_normal((streams, streams)) + 0.7 * np.triu(np.ones((streams, streams)), 1)
                 w["l%d.%s.in" % (i, q)][...] = rng.standard_normal(streams)
                 w["l%d.%s.out" % (i, q)][...] = rng.standard_normal(streams)
     cfg = model([recurrent(dense(24)), differential(dense(16), heads=2, kv_heads=1, dim=8, vdim=8)], width=40, vocab=70, streams=streams)
@@ -422,7 +422,7 @@ def sharp_model(tmp, kind, vocab=1024, window=40):
     if kind == "windowed":
         layer = windowed(None, heads=2, kv_heads=1, dim=16, vdim=16, scale=2.0, rot_dims=4, window=window, conv=3)
     else:
-        layer = differential(None, heads=2, kv_heads=1, dim=16, vdim=16, scale=2.0, diff=0.3, q_temp=(0.2, 64))
+        layer = differential(None, heads=2, kv_heads=1, dim=64, vdim=16, scale=1.5, diff=0.3, q_temp=(0.2, 64))
     cfg = model([layer], width=2 * HALF, vocab=vocab, streams=2)
     p = "l0.mix."
 
@@ -441,9 +441,9 @@ def sharp_model(tmp, kind, vocab=1024, window=40):
             q[:, :4] *= 0.05                                      # the rotated dimensions carry little
             w[p + "k"][:4] *= 0.05
         else:
-            k = w[p + "k"].reshape(1, 2, 16, 2 * HALF)
+            k = w[p + "k"].reshape(1, 2, 64, 2 * HALF)           # 64 channels: one key among hundreds stands out
             k[..., HALF:] = 0.0
-            q = w[p + "q"].reshape(2, 2, 16, 2 * HALF)
+            q = w[p + "q"].reshape(2, 2, 64, 2 * HALF)
             q[..., :HALF] = 0.0
             q[:, 0, :, HALF:] = k[0, 0, :, :HALF]                 # the first map is sharp,
             q[:, 1, :, HALF:] = 0.02 * k[0, 1, :, :HALF]          # the second nearly even
