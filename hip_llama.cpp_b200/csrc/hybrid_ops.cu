@@ -1765,11 +1765,13 @@ extern "C" int tha_hyb_conv(void* stream, int dtype, const tha_rows_t* rows, con
   if (rows->n_rows < 1 || channels < 1) return THA_STATUS_SUCCESS;
   if (taps < 1) return THA_STATUS_INVALID_ARG;
   cudaStream_t s = (cudaStream_t)stream;
-  const int gy = rows->n_rows < 65535 ? rows->n_rows : 65535;
   const bool f32 = out_f32 || dtype == THA_DT_F32;
 #define CONV_GO(KF, KB, per)                                                                                                              \
   do {                                                                                                                                    \
-    const dim3 grid(ceil_div(ceil_div(channels, per), 128), gy);                                                                         \
+    const int gx = ceil_div(ceil_div(channels, per), 128);                                                                               \
+    /* about eight blocks per SM: a block walks several rows with its taps in registers */                                               \
+    const int gy = min(rows->n_rows, max(1, 148 * 8 / gx));                                                                               \
+    const dim3 grid(gx, gy);                                                                                                              \
     if (f32) THA_CUDA_OK(launch(KF, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act, add_input, \
                                 (float*)out));                                                                                            \
     else THA_CUDA_OK(launch(KB, grid, dim3(128), 0, s, false, *rows, *st, conv_state_off, proj, ldp, col0, channels, taps, w, act, add_input,     \
