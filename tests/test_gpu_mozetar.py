@@ -273,6 +273,18 @@ def test_mixture_router_groups(tmp_path, experts, top, groups):
         assert rel_err(O.forward(free, b.w, tokens_for(b, 80, 9))[0], z) > 1e-2
 
 
+def test_prompt_sized_steps_give_each_expert_its_own_product(tmp_path):
+    """a step of more than a thousand rows whose experts get a thousand rows each takes, in bfloat16, one tensor-core product per
+    expert over gathered rows; every expert is chosen here, so no choice can flip"""
+    b = one_layer(tmp_path, recurrent(moe(experts=2, top=2, ff=64, groups=None), heads=2, dim=16, vdim=16), width=64)
+    toks = tokens_for(b, 1100, 3)
+    z, _ = b.ref(toks)
+    got = b.engine("bfloat16", max_tokens=1152).step([("a", toks, list(range(1100)))])
+    assert rel_err(got, z) < BF16_TOL
+    assert max(rel_err(got[p], z[p]) for p in range(0, 1100, 7)) < 3 * BF16_TOL
+    assert rel_err(feed(b.engine("bfloat16", max_tokens=1152), "a", toks, [500, 1]), z) < BF16_TOL
+
+
 @pytest.mark.parametrize("streams", [1, 2, 4, 5])
 def test_residual_streams(tmp_path, streams):
     """mixing matrices far from the identity and not symmetric: [from, to] and [to, from] differ by tens of percent"""
