@@ -1441,28 +1441,40 @@ __global__ void hyb_ff_act_vec_kernel(T* __restrict__ y, const float* __restrict
   hyb_store(dst, v0); hyb_store(dst + 1, v1); hyb_store(dst + 2, v2); hyb_store(dst + 3, v3);
 }
 
-// counting sort of the (row, pick) pairs by expert, one block, a warp per expert: within an expert the pairs stay in
-// ascending (row, pick) order, so the placement is the same on every run.
-__global__ void hyb_route_sort_kernel(int experts, int top, int n_rows, const int* __restrict__ expert_id, const int* __restrict__ counts,
-                                      int* __restrict__ group_off, int* __restrict__ sorted_row, int* __restrict__ inv) {
-  extern __shared__ int smi[];   // [experts + 1]
-  if (threadIdx.x == 0) {
+// counting sort of the (row, pick) pairs by expert, a block per expert: within an expert the pairs stay in ascending
+// (row, pick) order, so the placement is the same on every run.  The block finds its expert's first place from the counts,
+// then walks all pairs in chunks of its size: a ballot per warp, the warps' counts through shared memory, a pair's place =
+// what the expert has so far + the hits of the warps before + the hits of the lanes before.
+__global__ void __launch_bounds__(1024) hyb_route_sort_kernel(int experts, int top, int n_rows, const int* __restrict__ expert_id,
+                                                              const int* __restrict__ counts, int* __restrict__ group_off,
+                                                              int* __restrict__ sorted_row, int* __restrict__ inv) {
+  __shared__ int wcount[32];
+  __shared__ int s_start;
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (warp == 0) {
     int acc = 0;
-    for (int e = 0; e < experts; e++) { smi[e] = acc; group_off[e] = acc; acc += counts[e]; }
-    group_off[experts] = acc;
+    for (int x = lane; x < e; x += 32) acc += counts[x];
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(THA_FULL_MASK, acc, o);
+    if (lane == 0) {
+      s_start = acc;
+      group_off[e] = acc;
+      if (e == experts - 1) group_off[experts] = acc + counts[e];
+    }
   }
   __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  int at = s_start;
   const int n = n_rows * top;
-  for (int e = warp; e < experts; e += nwarps) {
-    int at = smi[e];
-    for (int i0 = 0; i0 < n; i0 += 32) {
-      const int i = i0 + lane;
-      const bool hit = i < n && expert_id[i] == e;
-      const unsigned m = __ballot_sync(THA_FULL_MASK, hit);
-      if (hit) { const int p = at + __popc(m & ((1u << lane) - 1)); sorted_row[p] = i / top; inv[i] = p; }
-      at += __popc(m);
-    }
+  for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    const bool hit = i < n && expert_id[i] == e;
+    const unsigned m = __ballot_sync(THA_FULL_MASK, hit);
+    if (lane == 0) wcount[warp] = __popc(m);
+    __syncthreads();
+    int before = 0, total = 0;
+    for (int w = 0; w < nwarps; w++) { const int c = wcount[w]; total += c; if (w < warp) before += c; }
+    if (hit) { const int p = at + before + __popc(m & ((1u << lane) - 1)); sorted_row[p] = i / top; inv[i] = p; }
+    at += total;
+    __syncthreads();
   }
 }
 
@@ -1844,9 +1856,10 @@ extern "C" int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* 
     THA_CUDA_OK(launch(hyb_route_kernel, dim3(ceil_div(n_rows, 4)), dim3(128), 0, s, false, e->experts, e->top, e->o_router, proj, ldp, n_rows,
                        expert_id, weight, counts));
   }
-  const int nt = 32 * (e->experts < 32 ? e->experts : 32);
-  THA_CUDA_OK(launch(hyb_route_sort_kernel, dim3(1), dim3(nt), sizeof(int) * (e->experts + 1), s, false, e->experts, e->top, n_rows,
-                     (const int*)expert_id, (const int*)counts, group_off, sorted_row, inv));
+  int nt = 64;
+  while (nt < 1024 && nt < n_rows * e->top) nt *= 2;
+  THA_CUDA_OK(launch(hyb_route_sort_kernel, dim3(e->experts), dim3(nt), 0, s, false, e->experts, e->top, n_rows, (const int*)expert_id,
+                     (const int*)counts, group_off, sorted_row, inv));
   return THA_STATUS_SUCCESS;
 }
 

@@ -152,26 +152,39 @@ __global__ void __launch_bounds__(512) hyb_streams_kernel(StreamsArgs a, T* __re
   }
 }
 
-template <typename T>
+template <typename T, int V>
 __global__ void __launch_bounds__(256) hyb_polynorm_kernel(T* __restrict__ y, const float* __restrict__ gu, long long ldg, int col_u,
                                                            const float* __restrict__ bias, float c0, float c1, float c2, float c3, float eps, int ff) {
   __shared__ float red[33];
   const size_t r = blockIdx.x;
   const float* z = gu + r * ldg + col_u;
   float s2 = 0.f, s4 = 0.f, s6 = 0.f;
-  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
-    const float v = z[i] + (bias ? bias[i] : 0.f), v2 = v * v;
-    s2 += v2;
-    s4 = fmaf(v2, v2, s4);
-    s6 = fmaf(v2 * v, v2 * v, s6);
+  for (int i = V * threadIdx.x; i < ff; i += V * blockDim.x) {
+    float v[V], b[V];
+    ldv<V>(z + i, v);
+    if (bias) ldv<V>(bias + i, b);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+      const float x = v[k] + (bias ? b[k] : 0.f), x2 = x * x;
+      s2 += x2;
+      s4 = fmaf(x2, x2, s4);
+      s6 = fmaf(x2 * x, x2 * x, s6);
+    }
   }
   s2 = block_sum(s2, red);
   s4 = block_sum(s4, red);
   s6 = block_sum(s6, red);
   const float i1 = c0 / sqrtf(s2 / (float)ff + eps), i2 = c1 / sqrtf(s4 / (float)ff + eps), i3 = c2 / sqrtf(s6 / (float)ff + eps);
-  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
-    const float v = z[i] + (bias ? bias[i] : 0.f), v2 = v * v;
-    hyb_store(y + r * ff + i, fmaf(i1, v, fmaf(i2, v2, fmaf(i3, v2 * v, c3))));
+  for (int i = V * threadIdx.x; i < ff; i += V * blockDim.x) {
+    float v[V], b[V], o[V];
+    ldv<V>(z + i, v);
+    if (bias) ldv<V>(bias + i, b);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+      const float x = v[k] + (bias ? b[k] : 0.f), x2 = x * x;
+      o[k] = fmaf(i1, x, fmaf(i2, x2, fmaf(i3, x2 * x, c3)));
+    }
+    stv<V>(y + r * ff + i, o);
   }
 }
 
@@ -249,11 +262,13 @@ extern "C" int tha_hyb_polynorm(void* stream, int dtype, void* y, const float* g
                                 float eps, int n, int ff) {
   if (n < 1 || ff < 1) return THA_STATUS_SUCCESS;
   cudaStream_t s = (cudaStream_t)stream;
-  const int nt = ff >= 1024 ? 256 : 128;
-  if (dtype == THA_DT_BF16)
-    THA_CUDA_OK(launch(hyb_polynorm_kernel<bf16>, dim3(n), dim3(nt), 0, s, false, (bf16*)y, gu, ldg, col_u, bias, c[0], c[1], c[2], c[3], eps, ff));
-  else
-    THA_CUDA_OK(launch(hyb_polynorm_kernel<float>, dim3(n), dim3(nt), 0, s, false, (float*)y, gu, ldg, col_u, bias, c[0], c[1], c[2], c[3], eps, ff));
+  const bool vec = ff % 4 == 0 && ldg % 4 == 0 && col_u % 4 == 0 && aligned16(gu) && aligned16(bias) && aligned16(y);
+  const int nt = ff >= (vec ? 4096 : 1024) ? 256 : 128;
+#define POLY_GO(T, V) \
+  THA_CUDA_OK(launch(hyb_polynorm_kernel<T, V>, dim3(n), dim3(nt), 0, s, false, (T*)y, gu, ldg, col_u, bias, c[0], c[1], c[2], c[3], eps, ff))
+  if (dtype == THA_DT_BF16) { if (vec) POLY_GO(bf16, 4); else POLY_GO(bf16, 1); }
+  else { if (vec) POLY_GO(float, 4); else POLY_GO(float, 1); }
+#undef POLY_GO
   return THA_STATUS_SUCCESS;
 }
 
