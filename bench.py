@@ -463,7 +463,7 @@ def parity_sample(args, cfg, host_w, e, B, n_slots=4, n_steps=8):
                 same_argmax = same_argmax and int(got[b].argmax()) == int(want.argmax())
     return {"slots": sample, "steps": n_steps, "max_abs_err": worst_abs, "max_err_over_max_logit": worst_rel,
             "argmax_identical": bool(same_argmax), "tolerance": "fp32: 1e-4 abs-or-rel (tests); Q8_0: see tests/test_gpu_baseline_shapes.py",
-            "checker": "oracle/_ref (%s compiled unmodified), untimed" % ("runq.c" if q8 else "run.cc")}
+            "oracle": "oracle/_ref (%s compiled unmodified), untimed" % ("runq.c" if q8 else "run.cc")}
 
 
 def resident_tok_s(e, cfg, B, W, K, device, pos0=0, seed=1):
@@ -841,7 +841,7 @@ def main():
                                         "sample": f"1 sequence x {done} greedy decode positions from pos 0, oracle/_ref "
                                                   f"({'runq.c' if args.quant == 'q8' else 'run.cc'} unmodified, "
                                                   f"{'-O3 -mavx2 -mfma' if fast else '-O2'}); run.cc has no OpenMP pragma"}
-            except Exception as ex:  # the checker being absent must not hide the GPU number
+            except Exception as ex:  # the oracle being absent must not hide the GPU number
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": f"unavailable: {ex}"}
         if tp_rec is not None:
             line.setdefault("extra", {})["tp_7b_q8_B64"] = tp_rec

@@ -1345,7 +1345,7 @@ __global__ void hyb_route_kernel(int experts, int top, int o_router, const float
 // Router with scores over ALL experts: s = softmax(z); the choice uses s + correction, limited to the `keep` groups (of
 // experts / groups neighbours each) whose largest choice score is highest -- experts outside them count as minus infinity,
 // whatever the sign of their score; the weights are the chosen s over their sum.  A warp per row; ties go to the lowest
-// index; needs top <= 32 and groups <= 32 (lane g keeps group g's best).
+// index; needs top <= 32 and at most 4096 experts (blocks of 128 threads).
 __global__ void hyb_route_groups_kernel(int experts, int top, int groups, int keep, int o_router, const float* __restrict__ correction,
                                         const float* __restrict__ proj, long long ldp, int n_rows, int* __restrict__ expert_id,
                                         float* __restrict__ weight, int* __restrict__ counts) {
@@ -1358,22 +1358,34 @@ __global__ void hyb_route_groups_kernel(int experts, int top, int groups, int ke
   float den = 0.f;
   for (int e = lane; e < experts; e += 32) den += expf(z[e] - zmax);
   den = warp_sum(den);
-  unsigned allowed = 0xffffffffu;   // bit g: group g may be chosen from
+  // bit g of the warp's words: group g may be chosen from (shared memory, so that any number of groups up to the experts fits)
+  __shared__ unsigned allowed_s[4][128];
+  unsigned* allowed = allowed_s[threadIdx.x >> 5];
   const int per = groups > 1 ? experts / groups : experts;
-  if (groups > 1 && keep < groups) {
-    float gbest = -INFINITY;         // lane g: the largest choice score of group g
-    if (lane < groups)
-      for (int e = lane * per; e < (lane + 1) * per; e++) gbest = fmaxf(gbest, expf(z[e] - zmax) / den + (correction ? correction[e] : 0.f));
-    allowed = 0u;
+  const bool bound = groups > 1 && keep < groups;
+  for (int w = lane; w < 128; w += 32) allowed[w] = bound ? 0u : 0xffffffffu;
+  __syncwarp();
+  if (bound) {
+    auto group_best = [&](int g) {   // the largest choice score of group g
+      float b = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; e++) b = fmaxf(b, expf(z[e] - zmax) / den + (correction ? correction[e] : 0.f));
+      return b;
+    };
+    const float gbest = lane < groups ? group_best(lane) : -INFINITY;   // lane g keeps group g's; groups beyond 32 are recomputed
     for (int j = 0; j < keep; j++) {
-      float best = (lane < groups && !((allowed >> lane) & 1u)) ? gbest : -INFINITY;
-      int bi = (lane < groups && !((allowed >> lane) & 1u)) ? lane : 0x7fffffff;
+      float best = -INFINITY; int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        if ((allowed[g >> 5] >> (g & 31)) & 1u) continue;
+        const float v = g < 32 ? gbest : group_best(g);
+        if (v > best || (v == best && g < bi)) { best = v; bi = g; }
+      }
       for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(THA_FULL_MASK, best, o);
         const int oi = __shfl_xor_sync(THA_FULL_MASK, bi, o);
         if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
       }
-      if (bi < groups) allowed |= 1u << bi;
+      if (lane == 0 && bi < groups) allowed[bi >> 5] |= 1u << (bi & 31);
+      __syncwarp();
     }
   }
   float sum = 0.f, mine = 0.f;
@@ -1383,7 +1395,8 @@ __global__ void hyb_route_groups_kernel(int experts, int top, int groups, int ke
     float best = -INFINITY, bs = 0.f; int bi = 0x7fffffff;
     for (int e = lane, n = 0; e < experts; e += 32, n++) {
       const bool taken = n < 64 ? (taken_lo >> n) & 1ull : (taken_hi >> (n - 64)) & 1ull;
-      if (taken || !((allowed >> (groups > 1 ? e / per : 0)) & 1u)) continue;
+      const int g = groups > 1 ? e / per : 0;
+      if (taken || !((allowed[g >> 5] >> (g & 31)) & 1u)) continue;
       const float sc = expf(z[e] - zmax) / den;
       const float v = sc + (correction ? correction[e] : 0.f);
       if (v > best || (v == best && e < bi)) { best = v; bi = e; bs = sc; }
@@ -1849,7 +1862,7 @@ extern "C" int tha_hyb_moe_route(void* stream, const tha_moe_t* e, const float* 
   THA_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int) * e->experts, s));
   if (e->route == THA_ROUTE_SOFTMAX_GROUPS) {
     const int groups = e->groups > 1 ? e->groups : 1;
-    if (groups > 32 || e->experts % groups || e->experts > 4096 || e->keep_groups < 1) return THA_STATUS_INVALID_ARG;
+    if (e->experts % groups || e->experts > 4096 || e->keep_groups < 1) return THA_STATUS_INVALID_ARG;
     THA_CUDA_OK(launch(hyb_route_groups_kernel, dim3(ceil_div(n_rows, 4)), dim3(128), 0, s, false, e->experts, e->top, groups,
                        e->keep_groups < groups ? e->keep_groups : groups, e->o_router, e->correction, proj, ldp, n_rows, expert_id, weight, counts));
   } else {

@@ -680,8 +680,8 @@ LayerModel* LayerModel::build(const LayerProgramSpec& spec, const SafeTensors& f
         E.act = e.act; E.route = e.route;
         if (e.route == THA_ROUTE_SOFTMAX_GROUPS) {
           const int groups = e.groups > 1 ? e.groups : 1, keep = e.groups > 1 ? e.keep_groups : 1;
-          if (groups > 32 || e.experts % groups || keep < 1 || keep > groups || e.experts > 4096)
-            throw std::runtime_error("mixture of experts: groups must divide the experts (at most 32 groups, 4096 experts), 1 <= keep <= groups");
+          if (e.experts % groups || keep < 1 || keep > groups || e.experts > 4096)
+            throw std::runtime_error("mixture of experts: groups must divide the experts (at most 4096 experts), 1 <= keep <= groups");
           if ((long long)keep * (e.experts / groups) < e.top) throw std::runtime_error("mixture of experts: the kept groups hold fewer experts than 'top'");
           E.groups = groups; E.keep_groups = keep;
           if (!e.correction.empty() && file.has(e.correction)) E.correction = vec(e.correction, e.experts);

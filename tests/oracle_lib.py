@@ -1,4 +1,4 @@
-"""ctypes bindings for the CHECKERS: oracle/liboracle.so (the CPU restatement) and,
+"""ctypes bindings for the ORACLES: oracle/liboracle.so (the CPU restatement) and,
 when present, oracle/_ref/*.so (the reference sources compiled unmodified).
 
 Test infrastructure only; nothing under hip_llama.cpp_b200/ may import this.

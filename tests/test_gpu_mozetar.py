@@ -260,7 +260,8 @@ def test_polynorm_feed_forward_alone(tmp_path):
     check_all_positions(b, n=40, dtype="bfloat16", tol=BF16_TOL)
 
 
-@pytest.mark.parametrize("experts,top,groups", [(8, 2, (4, 2)), (8, 3, (2, 1)), (6, 6, None), (9, 2, (3, 3)), (5, 1, (1, 1)), (12, 4, (6, 2))])
+@pytest.mark.parametrize("experts,top,groups", [(8, 2, (4, 2)), (8, 3, (2, 1)), (6, 6, None), (9, 2, (3, 3)), (5, 1, (1, 1)), (12, 4, (6, 2)),
+                                                (80, 3, (40, 2)), (66, 4, (66, 37)), (36, 2, (36, 36))])
 def test_mixture_router_groups(tmp_path, experts, top, groups):
     def tweak(w):
         w["l0.mix.o"][...] = 0.0
