@@ -312,8 +312,9 @@ def test_residual_streams(tmp_path, streams):
 
 
 def test_a_layer_that_reads_another_layers_cache_rows(tmp_path):
-    """layer 2 has no keys and values of its own: with rows of its own (or the rows of layer 1) the logits differ by percent"""
-    cfg = model([windowed(dense(24), window=14), windowed(None, window=30), windowed(dense(24), window=25, kv_from=0)], width=48, vocab=90)
+    """layer 2 has no keys and values of its own: with rows of its own (or the rows of layer 1) the logits differ by percent;
+    its query convolution has more taps than the convolutions of the layer whose rows it reads"""
+    cfg = model([windowed(dense(24), window=14), windowed(None, window=30), windowed(dense(24), window=25, conv=5, kv_from=0)], width=48, vocab=90)
     b = Built(tmp_path, cfg, 6)
     toks = tokens_for(b, 80, 2)
     z, layers = b.ref(toks)
