@@ -104,10 +104,10 @@ MOZETAR = {
 
 
 def mozetar_config(s: dict, n: dict) -> dict:
-    rot = {"base": 500000.0, "dims": s["dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}
+    rot = {"base": 500000.0, "dims": s["dim"] // 2, "scaling": {"factor": 16.0, "low": 1.0, "high": 2.0, "original": 4096}}
     win = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "conv": 4, "scale": s["dim"] ** -0.5,
            "mask": {"size": n["window"]}, "rot": rot}
-    dif = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": n["ddim"], "vdim": s["dim"], "scale": n["ddim"] ** -0.5, "diff": 0.6,
+    dif = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": n["ddim"], "vdim": s["dim"], "scale": n["ddim"] ** -0.5, "diff": 0.5,
            "q_temp": {"coef": 0.1, "every": 512}}
     rec = {"heads": n["gheads"], "dim": n["gdim"], "vdim": n["gvdim"]}
     moe = {"kind": "moe", "expert": {"ff": s["ff"]},
